@@ -1,0 +1,95 @@
+/* inferno_b200_attn.h -- C ABI of the B200 (sm_100a) causal-attention kernels.
+ *
+ * Drop-in boundary for the attention sub-path of K9Megahertz/Inferno.  The
+ * reference has no plugin or FFI mechanism; its operator API is source level
+ * (dtype-dispatch lambda -> raw pointers -> switch on device -> cuda_* launcher,
+ * e.g. src/inferno/core/ops.cpp:204-270), and its CUDA launchers are declared in
+ * src/inferno/cuda/cudaops.h:14-236 as plain functions over raw device pointers.
+ * The entry points below are what such a launcher for a fused attention op binds:
+ * raw device pointers, sizes and a stream; no C++ types, no exceptions, no exit().
+ *
+ * Layout of every tensor: dense row-major [B, H, T, D] (element strides
+ * H*T*D, T*D, D, 1), base address 16-byte aligned.  lse is dense [B, H, T] fp32.
+ * dtype selects the element type of q, k, v, o, dO, dq, dk, dv.
+ *
+ * All calls are asynchronous with respect to the host on `stream` and use the
+ * caller's current device; the library never calls cudaSetDevice and keeps no
+ * global handles.  Every function returns an ib200_status (0 = success).
+ */
+#ifndef INFERNO_B200_ATTN_H_
+#define INFERNO_B200_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Forward-declared so that the header needs no CUDA include; identical to the
+ * runtime's cudaStream_t. */
+typedef struct CUstream_st* ib200_stream_t;
+
+typedef enum {
+    IB200_OK = 0,
+    IB200_ERR_INVALID_ARGUMENT = 1, /* null pointer, non-positive size, bad enum */
+    IB200_ERR_UNSUPPORTED = 2,      /* head dim / dtype / mode the kernels do not implement */
+    IB200_ERR_MISALIGNED = 3,       /* a base pointer is not 16-byte aligned */
+    IB200_ERR_WORKSPACE = 4,        /* workspace missing or smaller than ib200_attn_workspace_bytes */
+    IB200_ERR_CUDA = 5,             /* a CUDA runtime/driver call failed (see ib200_last_cuda_error) */
+    IB200_ERR_DEVICE_TIMEOUT = 6,   /* a bounded device-side wait expired; outputs are invalid */
+    IB200_ERR_NO_DEVICE = 7         /* no sm_100 device is current */
+} ib200_status;
+
+enum { IB200_DTYPE_F32 = 0, IB200_DTYPE_BF16 = 1 };
+enum { IB200_MATH_TF32 = 0, IB200_MATH_3XTF32 = 1 }; /* fp32 I/O only; ignored for bf16 */
+enum { IB200_PASS_FWD = 0, IB200_PASS_BWD = 1 };
+
+/* Bytes of device scratch the forward (pass 0) or backward (pass 1) needs for
+ * this problem.  The caller owns the allocation; the library never allocates or
+ * frees device memory.  The first 256 bytes hold the device status word.
+ * Replaces nothing one-to-one: the reference's launchers cudaMalloc their own
+ * scratch per call (e.g. src/inferno/cuda/cudamaskedfill.cu:86-164). */
+int ib200_attn_workspace_bytes(int B, int H, int T, int D, int dtype, int pass, size_t* out_bytes);
+
+/* O = softmax(mask(Q K^T * scale)) V and lse = log-sum-exp of the masked, scaled
+ * scores of each row.  Replaces InfernoApp/main.cpp:737-754, i.e. the launch
+ * sequence cublas_mm_strided_batched_row_major (src/inferno/cuda/cudamatmul.cu:1114-1179),
+ * multiply_kernel_broadcast (cudamultiply.cu:16-47), cuda_triu_kernel (cudatri.cu:8-47),
+ * masked_fill_kernel (cudamaskedfill.cu:23-73), softmax_strided_kernel
+ * (cudasoftmax.cu:52-97) and a second batched GEMM.  causal must be 0 or 1
+ * (the reference path is always causal). */
+int ib200_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                   int B, int H, int T, int D, float scale, int causal, int dtype, int math_mode,
+                   void* workspace, size_t workspace_bytes, ib200_stream_t stream);
+
+/* dQ, dK, dV from dO, recomputing P from q, k and the saved lse.  Replaces the
+ * reference's backward node chain MMBackward (src/inferno/gradfn/mmbackward.cpp:36-98)
+ * -> SoftmaxBackward (softmaxbackward.cpp:36-128, kernel cudasoftmax.cu:222-280)
+ * -> MultiplyBackward (multiplybackward.cpp:34-57) -> MMBackward, including the
+ * masked_fill backward the reference lacks (ops.cpp:1235-1289). */
+int ib200_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dO,
+                   const float* lse, void* dq, void* dk, void* dv,
+                   int B, int H, int T, int D, float scale, int causal, int dtype, int math_mode,
+                   void* workspace, size_t workspace_bytes, ib200_stream_t stream);
+
+/* Synchronises `stream`, then reads the device status word that the kernels of the
+ * last call using `workspace` left behind.  Returns IB200_OK, IB200_ERR_DEVICE_TIMEOUT
+ * (*device_code receives the site code of the wait that expired) or IB200_ERR_CUDA.
+ * The reference's counterpart is check_cuda() -> log + exit
+ * (src/inferno/cuda/cudaops.h:198-210); this library reports instead of exiting. */
+int ib200_attn_check(const void* workspace, ib200_stream_t stream, int* device_code);
+
+/* Human-readable name of a status value; never NULL. */
+const char* ib200_status_string(int status);
+
+/* cudaError_t value of the most recent failing CUDA call on this host thread (0 if none). */
+int ib200_last_cuda_error(void);
+
+/* ABI version: major * 1000 + minor. */
+int ib200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INFERNO_B200_ATTN_H_ */

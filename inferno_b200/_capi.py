@@ -1,0 +1,67 @@
+"""ctypes binding of the C ABI in ``include/inferno_b200_attn.h``.
+
+The library is required: importing this module where the shared object has not been
+built raises, and no operation falls back to another implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from . import build as _build
+
+OK = 0
+ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_MISALIGNED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE = range(1, 8)
+DTYPE_F32, DTYPE_BF16 = 0, 1
+MATH_TF32, MATH_3XTF32 = 0, 1
+PASS_FWD, PASS_BWD = 0, 1
+
+EXPORTS = (
+    "ib200_attn_workspace_bytes", "ib200_attn_fwd", "ib200_attn_bwd", "ib200_attn_check",
+    "ib200_status_string", "ib200_last_cuda_error", "ib200_version",
+)
+
+_lib = None
+
+
+class Ib200Error(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        super().__init__(f"{where}: {status_string(status)} (status {status})")
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        path = _build.LIB_PATH
+        if not os.path.isfile(path):
+            raise ImportError(
+                f"{path} is missing: build it with `python -m inferno_b200.build` (there is no fallback path)")
+        L = ctypes.CDLL(path)
+        vp, i, f, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+        L.ib200_attn_workspace_bytes.argtypes = [i, i, i, i, i, i, ctypes.POINTER(sz)]
+        L.ib200_attn_workspace_bytes.restype = i
+        L.ib200_attn_fwd.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, f, i, i, i, vp, sz, vp]
+        L.ib200_attn_fwd.restype = i
+        L.ib200_attn_bwd.argtypes = [vp] * 9 + [i, i, i, i, f, i, i, i, vp, sz, vp]
+        L.ib200_attn_bwd.restype = i
+        L.ib200_attn_check.argtypes = [vp, vp, ctypes.POINTER(i)]
+        L.ib200_attn_check.restype = i
+        L.ib200_status_string.argtypes = [i]
+        L.ib200_status_string.restype = ctypes.c_char_p
+        L.ib200_last_cuda_error.restype = i
+        L.ib200_version.restype = i
+        _lib = L
+    return _lib
+
+
+def status_string(status: int) -> str:
+    return lib().ib200_status_string(int(status)).decode()
+
+
+def workspace_bytes(B: int, H: int, T: int, D: int, dtype: int, pass_: int) -> int:
+    out = ctypes.c_size_t(0)
+    rc = lib().ib200_attn_workspace_bytes(B, H, T, D, dtype, pass_, ctypes.byref(out))
+    if rc != OK:
+        raise Ib200Error(rc, "ib200_attn_workspace_bytes")
+    return int(out.value)

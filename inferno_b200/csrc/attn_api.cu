@@ -1,0 +1,216 @@
+// C ABI of the attention kernels (declared in include/inferno_b200_attn.h).
+// Host side only: argument checks, tensor maps, workspace carving and launches.
+#include "../../include/inferno_b200_attn.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include "attn_aux.cuh"
+#include "attn_bwd.cuh"
+#include "attn_fwd.cuh"
+
+namespace {
+
+using namespace ib200;
+
+thread_local int g_last_cuda_error = 0;
+
+inline bool cuda_ok(cudaError_t e) {
+    if (e == cudaSuccess) return true;
+    g_last_cuda_error = static_cast<int>(e);
+    (void)cudaGetLastError();
+    return false;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+        (void)cudaGetLastError();
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// Tensor map over a dense [BH, T, D] tensor; box = [box_rows x 128 bytes], 128B swizzle.
+bool make_tmap(CUtensorMap* m, const void* base, bool f32, int D, int T, long BH, int box_rows) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return false;
+    const cuuint64_t es = f32 ? 4 : 2;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(BH)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * es, static_cast<cuuint64_t>(T) * D * es};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(box_rows), 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                     const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+constexpr size_t kHeaderBytes = 256;
+
+struct Problem {
+    long BH, N;        // heads, elements per tensor
+    bool f32;
+};
+
+int check_common(int B, int H, int T, int D, int dtype, int math_mode, int causal) {
+    if (B <= 0 || H <= 0 || T <= 0 || D <= 0) return IB200_ERR_INVALID_ARGUMENT;
+    if (dtype != IB200_DTYPE_F32 && dtype != IB200_DTYPE_BF16) return IB200_ERR_INVALID_ARGUMENT;
+    if (causal != 0 && causal != 1) return IB200_ERR_INVALID_ARGUMENT;
+    if (dtype == IB200_DTYPE_F32 && math_mode != IB200_MATH_TF32 && math_mode != IB200_MATH_3XTF32) return IB200_ERR_INVALID_ARGUMENT;
+    if (dtype == IB200_DTYPE_BF16 && D != 64 && D != 128) return IB200_ERR_UNSUPPORTED;
+    if (dtype == IB200_DTYPE_F32 && D != 64) return IB200_ERR_UNSUPPORTED;
+    if (dtype == IB200_DTYPE_F32 && math_mode == IB200_MATH_3XTF32) return IB200_ERR_UNSUPPORTED;
+    if (static_cast<long>(B) * H > 65535L * 32768L) return IB200_ERR_UNSUPPORTED;
+    return IB200_OK;
+}
+
+size_t fwd_ws_bytes(long N, bool f32) { return kHeaderBytes + (f32 ? 3 * round_up(N * 4, 256) : 0); }
+size_t bwd_ws_bytes(long N, long BH, int T, bool f32) {
+    return kHeaderBytes + round_up(N * 4, 256) /*dq accumulator*/ + round_up(static_cast<size_t>(BH) * T * 4, 256) /*delta*/ +
+           (f32 ? 4 * round_up(N * 4, 256) : 0);
+}
+
+int device_ok() {
+    int dev = 0;
+    if (!cuda_ok(cudaGetDevice(&dev))) return IB200_ERR_NO_DEVICE;
+    int major = 0;
+    if (!cuda_ok(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev))) return IB200_ERR_NO_DEVICE;
+    return major == 10 ? IB200_OK : IB200_ERR_NO_DEVICE;
+}
+
+template <class TR>
+int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int* status, long BH, int T,
+               float scale, int causal, cudaStream_t stream) {
+    CUtensorMap tq, tk, tv, to;
+    const bool f32 = TR::TF32;
+    if (!make_tmap(&tq, q, f32, TR::D, T, BH, 128) || !make_tmap(&tk, k, f32, TR::D, T, BH, 128) ||
+        !make_tmap(&tv, v, f32, TR::D, T, BH, 128) || !make_tmap(&to, o, f32, TR::D, T, BH, 128))
+        return IB200_ERR_CUDA;
+    if (!cuda_ok(cudaFuncSetAttribute(attn_fwd_kernel<TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::SMEM_BYTES)))
+        return IB200_ERR_CUDA;
+    FwdParams prm;
+    prm.lse = lse;
+    prm.status = status;
+    prm.T = T;
+    prm.BH = static_cast<int>(BH);
+    prm.causal = causal;
+    prm.scale_log2 = scale * 1.4426950408889634f;
+    const int pairs = (T + 255) / 256;
+    // grid.y is limited to 65535: fold the head index over y and z
+    dim3 grid(pairs, static_cast<unsigned>(BH), 1);
+    if (BH > 65535) return IB200_ERR_UNSUPPORTED;
+    attn_fwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tk, tv, to, prm);
+    return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ib200_version(void) { return 1000; }
+
+int ib200_last_cuda_error(void) { return g_last_cuda_error; }
+
+const char* ib200_status_string(int status) {
+    switch (status) {
+        case IB200_OK: return "ok";
+        case IB200_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case IB200_ERR_UNSUPPORTED: return "unsupported shape, dtype or mode";
+        case IB200_ERR_MISALIGNED: return "pointer not 16-byte aligned";
+        case IB200_ERR_WORKSPACE: return "workspace missing or too small";
+        case IB200_ERR_CUDA: return "CUDA call failed";
+        case IB200_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+        case IB200_ERR_NO_DEVICE: return "no sm_100 device is current";
+        default: return "unknown status";
+    }
+}
+
+int ib200_attn_workspace_bytes(int B, int H, int T, int D, int dtype, int pass, size_t* out_bytes) {
+    if (!out_bytes) return IB200_ERR_INVALID_ARGUMENT;
+    if (pass != IB200_PASS_FWD && pass != IB200_PASS_BWD) return IB200_ERR_INVALID_ARGUMENT;
+    int rc = check_common(B, H, T, D, dtype, IB200_MATH_TF32, 1);
+    if (rc != IB200_OK) return rc;
+    const long BH = static_cast<long>(B) * H;
+    const long N = BH * T * D;
+    const bool f32 = dtype == IB200_DTYPE_F32;
+    *out_bytes = pass == IB200_PASS_FWD ? fwd_ws_bytes(N, f32) : bwd_ws_bytes(N, BH, T, f32);
+    return IB200_OK;
+}
+
+int ib200_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H, int T, int D,
+                   float scale, int causal, int dtype, int math_mode, void* workspace, size_t workspace_bytes,
+                   ib200_stream_t stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (!q || !k || !v || !o || !lse) return IB200_ERR_INVALID_ARGUMENT;
+    int rc = check_common(B, H, T, D, dtype, math_mode, causal);
+    if (rc != IB200_OK) return rc;
+    if (!(scale > 0.f) || !isfinite(scale)) return IB200_ERR_INVALID_ARGUMENT;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(lse)) return IB200_ERR_MISALIGNED;
+    const long BH = static_cast<long>(B) * H;
+    const long N = BH * T * D;
+    const bool f32 = dtype == IB200_DTYPE_F32;
+    if (!workspace || !aligned16(workspace) || workspace_bytes < fwd_ws_bytes(N, f32)) return IB200_ERR_WORKSPACE;
+    rc = device_ok();
+    if (rc != IB200_OK) return rc;
+
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    int* status = reinterpret_cast<int*>(ws);
+    if (!cuda_ok(cudaMemsetAsync(ws, 0, kHeaderBytes, stream))) return IB200_ERR_CUDA;
+    if (f32) {
+        // operands rounded to TF32 (round-to-nearest) once, so the tensor core's truncation is exact
+        const size_t slab = round_up(N * 4, 256);
+        float* rq = reinterpret_cast<float*>(ws + kHeaderBytes);
+        float* rk = reinterpret_cast<float*>(ws + kHeaderBytes + slab);
+        float* rv = reinterpret_cast<float*>(ws + kHeaderBytes + 2 * slab);
+        rc = launch_round_tf32(static_cast<const float*>(q), rq, N, stream); if (rc) return rc;
+        rc = launch_round_tf32(static_cast<const float*>(k), rk, N, stream); if (rc) return rc;
+        rc = launch_round_tf32(static_cast<const float*>(v), rv, N, stream); if (rc) return rc;
+        return launch_fwd<FwdTraits<64, true>>(rq, rk, rv, o, lse, status, BH, T, scale, causal, stream);
+    }
+    if (D == 64) return launch_fwd<FwdTraits<64, false>>(q, k, v, o, lse, status, BH, T, scale, causal, stream);
+    return launch_fwd<FwdTraits<128, false>>(q, k, v, o, lse, status, BH, T, scale, causal, stream);
+}
+
+int ib200_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
+                   void* dq, void* dk, void* dv, int B, int H, int T, int D, float scale, int causal, int dtype,
+                   int math_mode, void* workspace, size_t workspace_bytes, ib200_stream_t stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (!q || !k || !v || !o || !dO || !lse || !dq || !dk || !dv) return IB200_ERR_INVALID_ARGUMENT;
+    int rc = check_common(B, H, T, D, dtype, math_mode, causal);
+    if (rc != IB200_OK) return rc;
+    if (!(scale > 0.f) || !isfinite(scale)) return IB200_ERR_INVALID_ARGUMENT;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dO) || !aligned16(lse) ||
+        !aligned16(dq) || !aligned16(dk) || !aligned16(dv))
+        return IB200_ERR_MISALIGNED;
+    const long BH = static_cast<long>(B) * H;
+    const long N = BH * T * D;
+    const bool f32 = dtype == IB200_DTYPE_F32;
+    if (!workspace || !aligned16(workspace) || workspace_bytes < bwd_ws_bytes(N, BH, T, f32)) return IB200_ERR_WORKSPACE;
+    rc = device_ok();
+    if (rc != IB200_OK) return rc;
+    return launch_bwd_all(q, k, v, o, dO, lse, dq, dk, dv, BH, T, D, scale, causal, f32,
+                          static_cast<uint8_t*>(workspace), stream);
+}
+
+int ib200_attn_check(const void* workspace, ib200_stream_t stream_, int* device_code) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (!workspace) return IB200_ERR_INVALID_ARGUMENT;
+    int code = 0;
+    if (!cuda_ok(cudaMemcpyAsync(&code, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream))) return IB200_ERR_CUDA;
+    if (!cuda_ok(cudaStreamSynchronize(stream))) return IB200_ERR_CUDA;
+    if (device_code) *device_code = code;
+    return code == 0 ? IB200_OK : IB200_ERR_DEVICE_TIMEOUT;
+}
+
+}  // extern "C"

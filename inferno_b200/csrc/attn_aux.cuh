@@ -1,0 +1,113 @@
+// Bandwidth-bound helper kernels around the attention main kernels:
+//   * round_tf32   fp32 -> fp32 rounded to TF32 (round-to-nearest), so that the
+//                  tensor core's mantissa truncation of fp32 operands is exact
+//   * delta        delta[row] = sum_d O[row,d] * dO[row,d]; this is the reference's
+//                  dot = sum_j dP_ij P_ij (src/inferno/gradfn/softmaxbackward.h:101-109)
+//                  rewritten so that it needs no [T,T] matrix
+//   * dq_finish    dQ = scale * accumulator, cast to the output type; the scale is
+//                  the reference's MultiplyBackward (src/inferno/gradfn/multiplybackward.cpp:34-57)
+// All are grid-stride, 16-byte vectorised and coalesced; grids are sized from the SM count.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ib200 {
+
+constexpr int kAuxThreads = 256;
+constexpr int kAuxBlocks = 148 * 8;
+
+__global__ void __launch_bounds__(kAuxThreads) round_tf32_kernel(const float4* __restrict__ in, float4* __restrict__ out, long n4) {
+    for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n4; i += static_cast<long>(gridDim.x) * blockDim.x) {
+        float4 v = in[i];
+        uint32_t a, b, c, d;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(a) : "f"(v.x));
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(b) : "f"(v.y));
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(c) : "f"(v.z));
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(d) : "f"(v.w));
+        out[i] = make_float4(__uint_as_float(a), __uint_as_float(b), __uint_as_float(c), __uint_as_float(d));
+    }
+}
+
+inline int launch_round_tf32(const float* in, float* out, long n, cudaStream_t stream) {
+    const long n4 = n / 4;
+    const int blocks = static_cast<int>(n4 / kAuxThreads + 1 < kAuxBlocks ? n4 / kAuxThreads + 1 : kAuxBlocks);
+    round_tf32_kernel<<<blocks, kAuxThreads, 0, stream>>>(reinterpret_cast<const float4*>(in), reinterpret_cast<float4*>(out), n4);
+    return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+
+// One row of D elements is covered by TPR threads, each loading 16 bytes of O and of dO.
+template <int D, bool F32>
+__global__ void __launch_bounds__(kAuxThreads) delta_kernel(const void* __restrict__ o_, const void* __restrict__ do_, float* __restrict__ delta, long rows) {
+    constexpr int EPT = F32 ? 4 : 8;              // elements per 16-byte load
+    constexpr int TPR = D / EPT;                  // threads per row (8 or 16)
+    constexpr int RPB = kAuxThreads / TPR;        // rows per block per step
+    const int sub = threadIdx.x % TPR;
+    const long row0 = blockIdx.x * static_cast<long>(RPB) + threadIdx.x / TPR;
+    for (long row = row0; row < rows; row += static_cast<long>(gridDim.x) * RPB) {
+        float acc = 0.f;
+        if constexpr (F32) {
+            const float4 a = reinterpret_cast<const float4*>(o_)[row * TPR + sub];
+            const float4 b = reinterpret_cast<const float4*>(do_)[row * TPR + sub];
+            acc = a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+        } else {
+            const uint4 a = reinterpret_cast<const uint4*>(o_)[row * TPR + sub];
+            const uint4 b = reinterpret_cast<const uint4*>(do_)[row * TPR + sub];
+            const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+            const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 fa = __bfloat1622float2(pa[e]), fb = __bfloat1622float2(pb[e]);
+                acc = fmaf(fa.x, fb.x, acc);
+                acc = fmaf(fa.y, fb.y, acc);
+            }
+        }
+#pragma unroll
+        for (int off = TPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        if (sub == 0) delta[row] = acc;
+    }
+}
+
+template <int D, bool F32>
+inline int launch_delta(const void* o, const void* dO, float* delta, long rows, cudaStream_t stream) {
+    constexpr int RPB = kAuxThreads / (D / (F32 ? 4 : 8));
+    // every thread of a block takes part in the shuffles: the row loop bound is uniform per TPR group
+    long blocks = (rows + RPB - 1) / RPB;
+    if (blocks > kAuxBlocks) blocks = kAuxBlocks;
+    delta_kernel<D, F32><<<static_cast<int>(blocks), kAuxThreads, 0, stream>>>(o, dO, delta, rows);
+    return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+
+// out[i] = scale * acc[i], 8 elements per thread.
+template <bool F32>
+__global__ void __launch_bounds__(kAuxThreads) dq_finish_kernel(const float4* __restrict__ acc, void* __restrict__ out, float scale, long n8) {
+    for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
+        float4 a = acc[2 * i], b = acc[2 * i + 1];
+        a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
+        b.x *= scale; b.y *= scale; b.z *= scale; b.w *= scale;
+        if constexpr (F32) {
+            reinterpret_cast<float4*>(out)[2 * i] = a;
+            reinterpret_cast<float4*>(out)[2 * i + 1] = b;
+        } else {
+            uint4 v;
+            __nv_bfloat162 t;
+            t = __floats2bfloat162_rn(a.x, a.y); v.x = *reinterpret_cast<uint32_t*>(&t);
+            t = __floats2bfloat162_rn(a.z, a.w); v.y = *reinterpret_cast<uint32_t*>(&t);
+            t = __floats2bfloat162_rn(b.x, b.y); v.z = *reinterpret_cast<uint32_t*>(&t);
+            t = __floats2bfloat162_rn(b.z, b.w); v.w = *reinterpret_cast<uint32_t*>(&t);
+            reinterpret_cast<uint4*>(out)[i] = v;
+        }
+    }
+}
+
+template <bool F32>
+inline int launch_dq_finish(const float* acc, void* out, float scale, long n, cudaStream_t stream) {
+    const long n8 = n / 8;
+    long blocks = n8 / kAuxThreads + 1;
+    if (blocks > kAuxBlocks) blocks = kAuxBlocks;
+    dq_finish_kernel<F32><<<static_cast<int>(blocks), kAuxThreads, 0, stream>>>(reinterpret_cast<const float4*>(acc), out, scale, n8);
+    return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+
+}  // namespace ib200

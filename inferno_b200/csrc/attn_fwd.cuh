@@ -1,0 +1,357 @@
+// Causal flash-attention forward for sm_100a.
+//
+// Replaces the reference's composed forward
+//   matmul(q,kt) -> * scale -> triu/masked_fill(-1e9) -> Softmax -> matmul(attn,v)
+// (InfernoApp/main.cpp:737-754; ops in src/inferno/core/ops.cpp:437-735, 204-270,
+// 1235-1289, 1355-1398; src/inferno/functional/softmax.cpp:22-79) with one kernel
+// that never materialises the [T,T] score matrix and saves the per-row
+// log-sum-exp for the backward pass.
+//
+// One CTA owns two adjacent 128-row query tiles of one (batch, head) and walks the
+// key/value tiles up to the diagonal:
+//   warps 10-11 idle (they only donate registers)
+//   warp 9      TMA producer: Q tiles once, then K_j / V_j into two rings
+//   warp 8      MMA issuer (one lane): S_i = Q_i K_j^T (smem x smem -> TMEM) and
+//               O_i += P_i V_j (P read from TMEM, V from smem, MN-major)
+//   warps 0-3   softmax for query tile 0 (one thread per row, no shuffles needed:
+//               the 32x32b TMEM load gives each thread a whole row)
+//   warps 4-7   softmax for query tile 1
+// While one softmax group exponentiates, the tensor core works for the other.
+// P overwrites S in place in TMEM.  O stays in TMEM for the whole walk; it is
+// rescaled only when a row maximum grows by more than 2^kRescaleLog2 ("lazy"
+// rescale), which the final division by the row sum makes exact.
+#pragma once
+
+#include "sm100_ptx.cuh"
+
+namespace ib200 {
+
+template <int D_, bool TF32_>
+struct FwdTraits {
+    static constexpr int D = D_;
+    static constexpr bool TF32 = TF32_;
+    static constexpr int ES = TF32 ? 4 : 2;                 // operand element size
+    static constexpr int OUT_ES = TF32 ? 4 : 2;             // output element size
+    static constexpr int BM = 128, BN = 128;                // query / key tile rows
+    static constexpr int PANEL_ELEMS = 128 / ES;            // elements per 128-byte swizzle row
+    static constexpr int NP = D * ES / 128;                 // 128-byte column panels per tile
+    static constexpr int PANEL_BYTES = 128 * 128;           // [128 rows x 128 B]
+    static constexpr int TILE_BYTES = NP * PANEL_BYTES;
+    static constexpr int UMMA_K = 32 / ES;                  // elements per MMA k-step
+    static constexpr int S_KSTEPS = D / UMMA_K;             // k-steps of Q K^T
+    static constexpr int KSTEPS_PER_PANEL = 4;              // 128 B / 32 B
+    static constexpr int PV_KSTEPS = BN / UMMA_K;           // k-steps of P V
+    static constexpr int PV_KSTEP_BYTES = UMMA_K * 128;     // UMMA_K key rows of 128 B
+    static constexpr int P_COLS = BN * ES / 4;              // TMEM columns holding P
+    static constexpr int KV_STAGES = (TILE_BYTES <= 16384) ? 4 : 2;
+    static constexpr uint32_t FMT = TF32 ? kFmtTF32 : kFmtBF16;
+    static constexpr uint32_t IDESC_S = make_idesc(FMT, BM, BN, kMajorK, kMajorK);
+    static constexpr uint32_t IDESC_PV = make_idesc(FMT, BM, D, kMajorK, kMajorMN);
+    // TMEM columns: S0, S1 (128 each), O0, O1 (D each, padded to 128)
+    static constexpr uint32_t TM_S0 = 0, TM_S1 = 128, TM_O0 = 256, TM_O1 = 384, TM_COLS = 512;
+    static constexpr int SMEM_TILES = 2 + 2 * KV_STAGES;
+    static constexpr int SMEM_BYTES = SMEM_TILES * TILE_BYTES + 1024 /*align slack*/ + 512 /*barriers*/;
+    static constexpr int THREADS = 384;                      // 3 warpgroups: softmax 0, softmax 1, {MMA, TMA, 2 idle}
+};
+
+struct FwdParams {
+    float* lse;            // [BH, T] natural-log units, scale included
+    int* status;           // device status word (0 = ok)
+    int T, BH;
+    int causal;
+    float scale_log2;      // scale * log2(e)
+};
+
+constexpr float kRescaleLog2 = 8.0f;
+
+template <class TR>
+__device__ __forceinline__ void fwd_issue_s(uint32_t tmem_s, uint32_t q_saddr, uint32_t k_saddr) {
+#pragma unroll
+    for (int k = 0; k < TR::S_KSTEPS; ++k) {
+        const uint32_t off = (k / TR::KSTEPS_PER_PANEL) * TR::PANEL_BYTES + (k % TR::KSTEPS_PER_PANEL) * 32;
+        const uint64_t ad = make_sdesc_sw128(q_saddr + off, 16, 1024);
+        const uint64_t bd = make_sdesc_sw128(k_saddr + off, 16, 1024);
+        if constexpr (TR::TF32) umma_ss_tf32(tmem_s, ad, bd, TR::IDESC_S, k > 0);
+        else umma_ss_f16(tmem_s, ad, bd, TR::IDESC_S, k > 0);
+    }
+}
+
+template <class TR>
+__device__ __forceinline__ void fwd_issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t v_saddr, bool first_tile) {
+#pragma unroll
+    for (int k = 0; k < TR::PV_KSTEPS; ++k) {
+        const uint64_t bd = make_sdesc_sw128(v_saddr + k * TR::PV_KSTEP_BYTES, TR::PANEL_BYTES, 1024);
+        const uint32_t acc = (!first_tile || k > 0) ? 1u : 0u;
+        if constexpr (TR::TF32) umma_ts_tf32(tmem_o, tmem_p + k * 8, bd, TR::IDESC_PV, acc);
+        else umma_ts_f16(tmem_o, tmem_p + k * 8, bd, TR::IDESC_PV, acc);
+    }
+}
+
+template <class TR>
+__global__ void __launch_bounds__(TR::THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, FwdParams prm) {
+    constexpr int D = TR::D, BM = TR::BM, BN = TR::BN, KS = TR::KV_STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* sQ = smem;                                   // 2 tiles (reused as O staging)
+    uint8_t* sK = sQ + 2 * TR::TILE_BYTES;                // KS tiles
+    uint8_t* sV = sK + KS * TR::TILE_BYTES;               // KS tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + KS * TR::TILE_BYTES);
+    uint64_t* q_full = bars;                // [1]
+    uint64_t* k_full = bars + 1;            // [KS]
+    uint64_t* k_empty = k_full + KS;        // [KS]
+    uint64_t* v_full = k_empty + KS;        // [KS]
+    uint64_t* v_empty = v_full + KS;        // [KS]
+    uint64_t* s_full = v_empty + KS;        // [2]
+    uint64_t* p_full = s_full + 2;          // [2]
+    uint64_t* o_full = p_full + 2;          // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int T = prm.T;
+    const int bh = blockIdx.y;
+    const int pair = (gridDim.x - 1) - blockIdx.x;          // heaviest (longest walk) first
+    const int m_tile[2] = {2 * pair, 2 * pair + 1};
+    const int n_kv_total = (T + BN - 1) / BN;
+    int n_kv[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const bool valid = m_tile[i] * BM < T;
+        n_kv[i] = !valid ? 0 : (prm.causal ? min(m_tile[i] + 1, n_kv_total) : n_kv_total);
+    }
+    const int n_iter = max(n_kv[0], n_kv[1]);
+    AbortCtx ab{abort_flag, prm.status};
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        mbar_init(q_full, 1);
+        for (int s = 0; s < KS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&o_full[i], 1); }
+        fence_mbar_init();
+    }
+    if (warp == 8) { tmem_alloc(tmem_slot, TR::TM_COLS); tmem_relinquish(); }
+    if (warp == 9 && lane == 0) { tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_o); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    // Register rebalancing between warpgroups (the launch gives every thread 168).
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    }
+    if (warp == 9) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            const int q_tiles = (n_kv[1] > 0) ? 2 : 1;
+            mbar_arrive_expect_tx(q_full, q_tiles * TR::TILE_BYTES);
+            for (int i = 0; i < q_tiles; ++i)
+                for (int p = 0; p < TR::NP; ++p)
+                    tma_load_3d(sQ + i * TR::TILE_BYTES + p * TR::PANEL_BYTES, &tm_q, q_full, p * TR::PANEL_ELEMS, m_tile[i] * BM, bh);
+            for (int j = 0; j < n_iter; ++j) {
+                const int s = j % KS;
+                const uint32_t ph = (j / KS) & 1;
+                mbar_wait(&k_empty[s], ph ^ 1, ab, 10);
+                mbar_arrive_expect_tx(&k_full[s], TR::TILE_BYTES);
+                for (int p = 0; p < TR::NP; ++p)
+                    tma_load_3d(sK + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, &tm_k, &k_full[s], p * TR::PANEL_ELEMS, j * BN, bh);
+                mbar_wait(&v_empty[s], ph ^ 1, ab, 11);
+                mbar_arrive_expect_tx(&v_full[s], TR::TILE_BYTES);
+                for (int p = 0; p < TR::NP; ++p)
+                    tma_load_3d(sV + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, &tm_v, &v_full[s], p * TR::PANEL_ELEMS, j * BN, bh);
+            }
+        }
+    } else if (warp == 8) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0 && n_iter > 0) {
+            const uint32_t tm_s[2] = {tmem + TR::TM_S0, tmem + TR::TM_S1};
+            const uint32_t tm_oo[2] = {tmem + TR::TM_O0, tmem + TR::TM_O1};
+            const uint32_t q_addr[2] = {smem_u32(sQ), smem_u32(sQ + TR::TILE_BYTES)};
+            mbar_wait(q_full, 0, ab, 20);
+            mbar_wait(&k_full[0], 0, ab, 21);
+            tc_fence_after_sync();
+            for (int i = 0; i < 2; ++i)
+                if (n_kv[i] > 0) { fwd_issue_s<TR>(tm_s[i], q_addr[i], smem_u32(sK)); umma_commit(&s_full[i]); }
+            umma_commit(&k_empty[0]);
+            for (int j = 0; j < n_iter; ++j) {
+                const int sv = j % KS;
+                const int sk_next = (j + 1) % KS;
+                const bool has_next = (j + 1) < n_iter;
+                if (has_next) mbar_wait(&k_full[sk_next], ((j + 1) / KS) & 1, ab, 22);
+                mbar_wait(&v_full[sv], (j / KS) & 1, ab, 23);
+                for (int i = 0; i < 2; ++i) {
+                    if (j < n_kv[i]) {
+                        mbar_wait(&p_full[i], j & 1, ab, 24);
+                        tc_fence_after_sync();
+                        fwd_issue_pv<TR>(tm_oo[i], tm_s[i], smem_u32(sV + sv * TR::TILE_BYTES), j == 0);
+                        umma_commit(&o_full[i]);
+                        if (j + 1 < n_kv[i]) {
+                            fwd_issue_s<TR>(tm_s[i], q_addr[i], smem_u32(sK + sk_next * TR::TILE_BYTES));
+                            umma_commit(&s_full[i]);
+                        }
+                    }
+                }
+                umma_commit(&v_empty[sv]);
+                if (has_next) umma_commit(&k_empty[sk_next]);
+            }
+        }
+    } else if (warp < 8) {
+        // ------------------------------ softmax groups ------------------------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        const int i = warp >> 2;                 // query tile handled by this group
+        const int t = tid & 127;                 // row inside the tile
+        const int wq = warp & 3;                 // TMEM lane quarter
+        const int nkv = n_kv[i];
+        const int row_g = m_tile[i] * BM + t;
+        const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+        const uint32_t tm_s = tmem + (i ? TR::TM_S1 : TR::TM_S0) + lane_base;
+        const uint32_t tm_oo = tmem + (i ? TR::TM_O1 : TR::TM_O0) + lane_base;
+        const float c = prm.scale_log2;
+        float m_used = 0.f, l = 0.f;
+
+        for (int j = 0; j < nkv; ++j) {
+            mbar_wait(&s_full[i], j & 1, ab, 30);
+            tc_fence_after_sync();
+            float s[BN];
+#pragma unroll
+            for (int cc = 0; cc < BN; cc += 32) {
+                uint32_t r[32];
+                tmem_ld_x32(tm_s + cc, r);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) s[cc + e] = __uint_as_float(r[e]);
+            }
+            tmem_wait_ld();
+            // masking: causal on the diagonal tile; keys past T on the last tile
+            const int col0 = j * BN;
+            const bool diag = prm.causal && (j == m_tile[i]);
+            const bool tail = (col0 + BN > T);
+            if (diag || tail) {
+                const int limit = diag ? min(row_g, T - 1) : (T - 1);   // last visible key
+#pragma unroll
+                for (int e = 0; e < BN; ++e)
+                    if (col0 + e > limit) s[e] = -INFINITY;
+            }
+            float mx = s[0];
+#pragma unroll
+            for (int e = 1; e < BN; ++e) mx = fmaxf(mx, s[e]);
+            float mx_s = mx * c;
+            if (mx == -INFINITY) mx_s = m_used;                    // fully masked row in this tile
+            if (j == 0) {
+                m_used = (mx == -INFINITY) ? 0.f : mx_s;
+            } else {
+                const bool need = mx_s > m_used + kRescaleLog2;
+                if (__any_sync(0xffffffffu, need)) {
+                    mbar_wait(&o_full[i], (j - 1) & 1, ab, 31);
+                    tc_fence_after_sync();
+                    const float alpha = need ? fast_exp2(m_used - mx_s) : 1.f;
+                    if (need) { m_used = mx_s; l *= alpha; }
+#pragma unroll
+                    for (int cc = 0; cc < D; cc += 32) {
+                        uint32_t r[32];
+                        tmem_ld_x32(tm_oo + cc, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+                        tmem_st_x32(tm_oo + cc, r);
+                    }
+                    tmem_wait_st();
+                }
+            }
+            float lsum = 0.f;
+            if constexpr (!TR::TF32) {
+#pragma unroll
+                for (int cc = 0; cc < BN; cc += 32) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const float p0 = fast_exp2(fmaf(s[cc + e], c, -m_used));
+                        const float p1 = fast_exp2(fmaf(s[cc + e + 1], c, -m_used));
+                        lsum += p0 + p1;
+                        pk[e >> 1] = pack_bf16x2(p0, p1);
+                    }
+                    tmem_st_x16(tm_s + (cc >> 1), pk);
+                }
+            } else {
+#pragma unroll
+                for (int cc = 0; cc < BN; cc += 32) {
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const float p0 = fast_exp2(fmaf(s[cc + e], c, -m_used));
+                        lsum += p0;
+                        uint32_t u;
+                        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(p0));
+                        pk[e] = u;
+                    }
+                    tmem_st_x32(tm_s + cc, pk);
+                }
+            }
+            l += lsum;
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[i]);
+        }
+
+        if (nkv > 0) {
+            mbar_wait(&o_full[i], (nkv - 1) & 1, ab, 32);
+            tc_fence_after_sync();
+            const float inv_l = 1.f / l;
+            uint8_t* stage = sQ + i * TR::TILE_BYTES;     // Q_i is dead once its last S MMA has completed
+#pragma unroll
+            for (int cc = 0; cc < D; cc += 32) {
+                uint32_t r[32];
+                tmem_ld_x32(tm_oo + cc, r);
+                tmem_wait_ld();
+                if constexpr (!TR::TF32) {
+                    // 32 columns = 64 bytes = 4 chunks of 16 B inside panel cc/64
+                    const int panel = cc / 64, chunk0 = (cc % 64) / 8;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 v;
+                        v.x = pack_bf16x2(__uint_as_float(r[q4 * 8 + 0]) * inv_l, __uint_as_float(r[q4 * 8 + 1]) * inv_l);
+                        v.y = pack_bf16x2(__uint_as_float(r[q4 * 8 + 2]) * inv_l, __uint_as_float(r[q4 * 8 + 3]) * inv_l);
+                        v.z = pack_bf16x2(__uint_as_float(r[q4 * 8 + 4]) * inv_l, __uint_as_float(r[q4 * 8 + 5]) * inv_l);
+                        v.w = pack_bf16x2(__uint_as_float(r[q4 * 8 + 6]) * inv_l, __uint_as_float(r[q4 * 8 + 7]) * inv_l);
+                        *reinterpret_cast<uint4*>(stage + panel * TR::PANEL_BYTES + sw128_offset(t, chunk0 + q4)) = v;
+                    }
+                } else {
+                    // 32 fp32 columns = one 128-byte panel row = 8 chunks of 16 B
+                    const int panel = cc / 32;
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; ++q4) {
+                        uint4 v;
+                        v.x = __float_as_uint(__uint_as_float(r[q4 * 4 + 0]) * inv_l);
+                        v.y = __float_as_uint(__uint_as_float(r[q4 * 4 + 1]) * inv_l);
+                        v.z = __float_as_uint(__uint_as_float(r[q4 * 4 + 2]) * inv_l);
+                        v.w = __float_as_uint(__uint_as_float(r[q4 * 4 + 3]) * inv_l);
+                        *reinterpret_cast<uint4*>(stage + panel * TR::PANEL_BYTES + sw128_offset(t, q4)) = v;
+                    }
+                }
+            }
+            if (row_g < T) prm.lse[static_cast<size_t>(bh) * T + row_g] = (m_used + log2f(l)) * 0.6931471805599453f;
+            fence_proxy_async_smem();
+            asm volatile("bar.sync %0, 128;" ::"r"(1 + i) : "memory");
+            if (t == 0) {
+                for (int p = 0; p < TR::NP; ++p)
+                    tma_store_3d(&tm_o, stage + p * TR::PANEL_BYTES, p * TR::PANEL_ELEMS, m_tile[i] * BM, bh);
+                tma_store_commit();
+                tma_store_wait_all();
+            }
+        }
+    }
+
+    // ------------------------------ tear-down ------------------------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag != 0) {
+        // a wait gave up: give any TMA copy still in flight time to land before the CTA's
+        // shared memory is released
+        for (int it = 0; it < 64; ++it) __nanosleep(1000);
+    }
+    if (warp == 8) tmem_dealloc(tmem, TR::TM_COLS);
+}
+
+}  // namespace ib200
