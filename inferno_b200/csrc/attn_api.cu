@@ -114,6 +114,56 @@ int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
     return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
 }
 
+
+template <class TR>
+int launch_bwd(const void* q, const void* k, const void* v, const void* dO, const float* lse, const float* delta,
+               float* dq_acc, void* dk, void* dv, int* status, long BH, int T, float scale, int causal,
+               cudaStream_t stream) {
+    CUtensorMap tq, tk, tv, tdo, tdk, tdv;
+    if (!make_tmap(&tq, q, false, TR::D, T, BH, TR::BQ) || !make_tmap(&tdo, dO, false, TR::D, T, BH, TR::BQ) ||
+        !make_tmap(&tk, k, false, TR::D, T, BH, TR::BKV) || !make_tmap(&tv, v, false, TR::D, T, BH, TR::BKV) ||
+        !make_tmap(&tdk, dk, false, TR::D, T, BH, TR::BKV) || !make_tmap(&tdv, dv, false, TR::D, T, BH, TR::BKV))
+        return IB200_ERR_CUDA;
+    if (!cuda_ok(cudaFuncSetAttribute(attn_bwd_kernel<TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::SMEM_BYTES)))
+        return IB200_ERR_CUDA;
+    BwdParams prm;
+    prm.lse = lse;
+    prm.delta = delta;
+    prm.dq_acc = dq_acc;
+    prm.status = status;
+    prm.T = T;
+    prm.BH = static_cast<int>(BH);
+    prm.causal = causal;
+    prm.scale = scale;
+    prm.scale_log2 = scale * 1.4426950408889634f;
+    if (BH > 65535) return IB200_ERR_UNSUPPORTED;
+    dim3 grid((T + TR::BKV - 1) / TR::BKV, static_cast<unsigned>(BH), 1);
+    attn_bwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdk, tdv, prm);
+    return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
+}
+
+// delta pre-pass -> main kernel -> dQ finish.  Workspace: [header | dq accumulator | delta | (fp32 only) operand copies].
+int launch_bwd_all(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
+                   void* dq, void* dk, void* dv, long BH, int T, int D, float scale, int causal, bool f32,
+                   uint8_t* ws, cudaStream_t stream) {
+    const long N = BH * T * D;
+    int* status = reinterpret_cast<int*>(ws);
+    float* dq_acc = reinterpret_cast<float*>(ws + kHeaderBytes);
+    float* delta = reinterpret_cast<float*>(ws + kHeaderBytes + round_up(N * 4, 256));
+    if (!cuda_ok(cudaMemsetAsync(ws, 0, kHeaderBytes + round_up(N * 4, 256), stream))) return IB200_ERR_CUDA;
+    if (f32) return IB200_ERR_UNSUPPORTED;
+    int rc;
+    if (D == 64) {
+        rc = launch_delta<64, false>(o, dO, delta, BH * T, stream); if (rc) return rc;
+        rc = launch_bwd<BwdTraits<64>>(q, k, v, dO, lse, delta, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
+    } else {
+        rc = launch_delta<128, false>(o, dO, delta, BH * T, stream); if (rc) return rc;
+        rc = launch_bwd<BwdTraits<128>>(q, k, v, dO, lse, delta, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
+    }
+    if (rc) return rc;
+    return launch_dq_finish<false>(dq_acc, dq, scale, N, stream);
+}
+
 }  // namespace
 
 extern "C" {

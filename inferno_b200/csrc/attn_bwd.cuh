@@ -1,7 +1,367 @@
+// Causal flash-attention backward for sm_100a.
+//
+// Replaces the reference's backward node chain for the attention sub-graph
+//   MMBackward(attn, v)   dP = dO V^T, dV = P^T dO      src/inferno/gradfn/mmbackward.cpp:36-98
+//   SoftmaxBackward       dS = P * (dP - rowsum(dP*P))  src/inferno/gradfn/softmaxbackward.cpp:36-128
+//   (masked_fill has no backward node in the reference; dS is 0 where masked because P is 0)
+//   MultiplyBackward      dS *= scale                   src/inferno/gradfn/multiplybackward.cpp:34-57
+//   MMBackward(q, kt)     dQ = dS K, dK = dS^T Q        src/inferno/gradfn/mmbackward.cpp:36-98
+// with a kernel that recomputes P from Q, K and the saved log-sum-exp instead of
+// reading a stored [T,T] matrix, and takes rowsum(dP*P) as delta = rowsum(dO*O).
+//
+// One CTA owns one 128-row key/value tile of one (batch, head) and walks the
+// 64-row query blocks at or below the diagonal.  Everything is computed
+// transposed (key index on the TMEM lanes) so that P^T and dS^T can feed the
+// dV / dK MMAs straight from TMEM:
+//   S^T  = K Q^T        smem x smem  -> TMEM ST[b]          (M=128 keys, N=64 queries)
+//   dP^T = V dO^T       smem x smem  -> TMEM DP[b]
+//   dV  += P^T dO       TMEM x smem (dO MN-major)   -> TMEM DV
+//   dK  += dS^T Q       TMEM x smem (Q MN-major)    -> TMEM DK
+//   dQ^T = K^T dS^T     smem (K MN-major) x smem (dS^T MN-major) -> TMEM DP[b]  (M=D, N=64)
+// dQ^T leaves through coalesced fp32 reductions into a scratch accumulator
+// (lane = head-dim index, so a warp adds 32 consecutive floats per instruction).
+//
+//   warps 0-7    compute: P^T = exp2(S^T c - lse), dS^T = P^T (dP^T - delta); each
+//                thread owns one key row; warps 0-3 take query columns 0-31, 4-7 take 32-63
+//   warps 8-11   drain dQ^T from TMEM to the global accumulator
+//   warp 12      TMA producer (K, V once; Q, dO, lse, delta per query block)
+//   warp 13      MMA issuer (one lane)
 #pragma once
-#include "sm100_ptx.cuh"
+
 #include "attn_aux.cuh"
+#include "sm100_ptx.cuh"
+
 namespace ib200 {
-inline int launch_bwd_all(const void*, const void*, const void*, const void*, const void*, const float*, void*, void*, void*,
-                          long, int, int, float, int, bool, uint8_t*, cudaStream_t) { return 2; }
+
+template <int D_>
+struct BwdTraits {
+    static constexpr int D = D_;
+    static constexpr int BKV = 128, BQ = 64;
+    static constexpr int NP = D * 2 / 128;                   // 128-byte column panels
+    static constexpr int KV_PANEL = BKV * 128, KV_TILE = NP * KV_PANEL;
+    static constexpr int Q_PANEL = BQ * 128, Q_TILE = NP * Q_PANEL;
+    static constexpr int DS_TILE = BKV * 128;                // [128 keys x 64 queries] bf16
+    static constexpr int NS = 3;                             // Q/dO ring depth
+    static constexpr int D_KSTEPS = D / 16;                  // k-steps over the head dim
+    static constexpr uint32_t IDESC_ST = make_idesc(kFmtBF16, BKV, BQ, kMajorK, kMajorK);
+    static constexpr uint32_t IDESC_DKV = make_idesc(kFmtBF16, BKV, D, kMajorK, kMajorMN);
+    static constexpr uint32_t IDESC_DQ = make_idesc(kFmtBF16, D, BQ, kMajorMN, kMajorMN);
+    static constexpr uint32_t TM_ST = 0, TM_DP = 128, TM_DV = 256, TM_DK = 384, TM_COLS = 512;
+    static constexpr int OFF_K = 0;
+    static constexpr int OFF_V = OFF_K + KV_TILE;
+    static constexpr int OFF_Q = OFF_V + KV_TILE;            // NS tiles; ring start, reused as dV/dK staging
+    static constexpr int OFF_DO = OFF_Q + NS * Q_TILE;       // NS tiles
+    static constexpr int OFF_DS = OFF_DO + NS * Q_TILE;      // 2 tiles
+    static constexpr int OFF_VEC = OFF_DS + 2 * DS_TILE;     // NS x (lse[64], delta[64]) floats
+    static constexpr int OFF_BAR = OFF_VEC + NS * 2 * BQ * 4;
+    static constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
+    static constexpr int THREADS = 512;
+    static_assert(2 * NS * Q_TILE >= 2 * KV_TILE, "epilogue staging must fit in the Q/dO ring");
+};
+
+struct BwdParams {
+    const float* lse;      // [BH, T]
+    const float* delta;    // [BH, T]
+    float* dq_acc;         // [BH, T, D] fp32, zeroed before launch
+    int* status;
+    int T, BH, causal;
+    float scale, scale_log2;
+};
+
+// TMEM column of the packed bf16 pair that starts k-step ks (16 queries) of P^T / dS^T:
+// queries 0-31 live in columns 0-15, queries 32-63 in columns 32-47 (each compute
+// warpgroup overwrites only the columns it has itself read).
+__device__ __forceinline__ uint32_t bwd_pcol(int ks) { return static_cast<uint32_t>((ks >> 1) * 32 + (ks & 1) * 8); }
+
+template <class TR>
+__global__ void __launch_bounds__(TR::THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv, BwdParams prm) {
+    constexpr int D = TR::D, BKV = TR::BKV, BQ = TR::BQ, NS = TR::NS;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* sK = smem + TR::OFF_K;
+    uint8_t* sV = smem + TR::OFF_V;
+    uint8_t* sQ = smem + TR::OFF_Q;
+    uint8_t* sDO = smem + TR::OFF_DO;
+    uint8_t* sDS = smem + TR::OFF_DS;
+    float* sVec = reinterpret_cast<float*>(smem + TR::OFF_VEC);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TR::OFF_BAR);
+    uint64_t* kv_full = bars;               // [1]
+    uint64_t* qdo_full = bars + 1;          // [NS]
+    uint64_t* qdo_empty = qdo_full + NS;    // [NS]
+    uint64_t* st_full = qdo_empty + NS;     // [2]
+    uint64_t* dp_full = st_full + 2;        // [2]
+    uint64_t* p_full = dp_full + 2;         // [2]
+    uint64_t* ds_full = p_full + 2;         // [2]
+    uint64_t* dq_full = ds_full + 2;        // [2]
+    uint64_t* dq_empty = dq_full + 2;       // [2]
+    uint64_t* dkv_full = dq_empty + 2;      // [1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dkv_full + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int T = prm.T;
+    const int bh = blockIdx.y;
+    const int n = blockIdx.x;                                   // key tile; tile 0 walks the most query blocks and starts first
+    const int nqb = (T + BQ - 1) / BQ;
+    const int m0 = prm.causal ? (n * BKV) / BQ : 0;             // first query block at or below the diagonal
+    const int nblk = nqb - m0;
+    AbortCtx ab{abort_flag, prm.status};
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        mbar_init(kv_full, 1);
+        for (int s = 0; s < NS; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&st_full[b], 1); mbar_init(&dp_full[b], 1); mbar_init(&p_full[b], 8); mbar_init(&ds_full[b], 8);
+            mbar_init(&dq_full[b], 1); mbar_init(&dq_empty[b], 4);
+        }
+        mbar_init(dkv_full, 1);
+        fence_mbar_init();
+    }
+    if (warp == 13) { tmem_alloc(tmem_slot, TR::TM_COLS); tmem_relinquish(); }
+    if (warp == 12 && lane == 0) {
+        tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_do);
+        tma_prefetch_desc(&tm_dk); tma_prefetch_desc(&tm_dv);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 12) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            mbar_arrive_expect_tx(kv_full, 2 * TR::KV_TILE);
+            for (int p = 0; p < TR::NP; ++p) {
+                tma_load_3d(sK + p * TR::KV_PANEL, &tm_k, kv_full, p * 64, n * BKV, bh);
+                tma_load_3d(sV + p * TR::KV_PANEL, &tm_v, kv_full, p * 64, n * BKV, bh);
+            }
+        }
+        for (int it = 0; it < nblk; ++it) {
+            const int s = it % NS;
+            const int m = m0 + it;
+            mbar_wait(&qdo_empty[s], ((it / NS) & 1) ^ 1, ab, 10);
+            // per-row vectors: lse pre-multiplied by log2(e); rows past T get +inf so that P = 0
+            float* v_lse = sVec + s * 2 * BQ;
+            float* v_del = v_lse + BQ;
+#pragma unroll
+            for (int e = lane; e < BQ; e += 32) {
+                const int qg = m * BQ + e;
+                const bool ok = qg < T;
+                v_lse[e] = ok ? prm.lse[static_cast<size_t>(bh) * T + qg] * 1.4426950408889634f : INFINITY;
+                v_del[e] = ok ? prm.delta[static_cast<size_t>(bh) * T + qg] : 0.f;
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&qdo_full[s], 2 * TR::Q_TILE);
+                for (int p = 0; p < TR::NP; ++p) {
+                    tma_load_3d(sQ + s * TR::Q_TILE + p * TR::Q_PANEL, &tm_q, &qdo_full[s], p * 64, m * BQ, bh);
+                    tma_load_3d(sDO + s * TR::Q_TILE + p * TR::Q_PANEL, &tm_do, &qdo_full[s], p * 64, m * BQ, bh);
+                }
+            }
+        }
+    } else if (warp == 13) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+            mbar_wait(kv_full, 0, ab, 20);
+            for (int it = 0; it <= nblk; ++it) {
+                const int b = it & 1, s = it % NS;
+                const uint32_t aQ = smem_u32(sQ + s * TR::Q_TILE), aDO = smem_u32(sDO + s * TR::Q_TILE);
+                if (it < nblk) {
+                    mbar_wait(&qdo_full[s], (it / NS) & 1, ab, 21);
+                    tc_fence_after_sync();
+                    // S^T(it) = K Q^T
+#pragma unroll
+                    for (int k = 0; k < TR::D_KSTEPS; ++k) {
+                        const uint64_t ad = make_sdesc_sw128(aK + (k / 4) * TR::KV_PANEL + (k % 4) * 32, 16, 1024);
+                        const uint64_t bd = make_sdesc_sw128(aQ + (k / 4) * TR::Q_PANEL + (k % 4) * 32, 16, 1024);
+                        umma_ss_f16(tmem + TR::TM_ST + b * 64, ad, bd, TR::IDESC_ST, k > 0);
+                    }
+                    umma_commit(&st_full[b]);
+                }
+                const int j = it - 1, bj = j & 1, sj = j % NS;
+                const uint32_t aQj = smem_u32(sQ + sj * TR::Q_TILE), aDOj = smem_u32(sDO + sj * TR::Q_TILE);
+                if (j >= 0) {
+                    // dV += P^T(j) dO(j)
+                    mbar_wait(&p_full[bj], (j >> 1) & 1, ab, 22);
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int ks = 0; ks < BQ / 16; ++ks) {
+                        const uint64_t bd = make_sdesc_sw128(aDOj + ks * 2048, TR::Q_PANEL, 1024);
+                        umma_ts_f16(tmem + TR::TM_DV, tmem + TR::TM_ST + bj * 64 + bwd_pcol(ks), bd, TR::IDESC_DKV, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    // dK += dS^T(j) Q(j)
+                    mbar_wait(&ds_full[bj], (j >> 1) & 1, ab, 23);
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int ks = 0; ks < BQ / 16; ++ks) {
+                        const uint64_t bd = make_sdesc_sw128(aQj + ks * 2048, TR::Q_PANEL, 1024);
+                        umma_ts_f16(tmem + TR::TM_DK, tmem + TR::TM_DP + bj * 64 + bwd_pcol(ks), bd, TR::IDESC_DKV, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                }
+                if (it < nblk) {
+                    // dP^T(it) = V dO^T, into the buffer the drain of dQ^T(it-2) has released
+                    if (it >= 2) { mbar_wait(&dq_empty[b], ((it - 2) >> 1) & 1, ab, 24); tc_fence_after_sync(); }
+#pragma unroll
+                    for (int k = 0; k < TR::D_KSTEPS; ++k) {
+                        const uint64_t ad = make_sdesc_sw128(aV + (k / 4) * TR::KV_PANEL + (k % 4) * 32, 16, 1024);
+                        const uint64_t bd = make_sdesc_sw128(aDO + (k / 4) * TR::Q_PANEL + (k % 4) * 32, 16, 1024);
+                        umma_ss_f16(tmem + TR::TM_DP + b * 64, ad, bd, TR::IDESC_ST, k > 0);
+                    }
+                    umma_commit(&dp_full[b]);
+                }
+                if (j >= 0) {
+                    // dQ^T(j) = K^T dS^T(j), over the dS^T/dP^T buffer that dK(j) has just consumed
+                    const uint32_t aDS = smem_u32(sDS + bj * TR::DS_TILE);
+#pragma unroll
+                    for (int ks = 0; ks < BKV / 16; ++ks) {
+                        const uint64_t ad = make_sdesc_sw128(aK + ks * 2048, TR::KV_PANEL, 1024);
+                        const uint64_t bd = make_sdesc_sw128(aDS + ks * 2048, 16, 1024);
+                        umma_ss_f16(tmem + TR::TM_DP + bj * 64, ad, bd, TR::IDESC_DQ, ks > 0);
+                    }
+                    umma_commit(&dq_full[bj]);
+                    umma_commit(&qdo_empty[sj]);
+                }
+            }
+            umma_commit(dkv_full);
+        }
+    } else if (warp < 8) {
+        // ------------------------------ compute: P^T and dS^T ------------------------------
+        const int h = warp >> 2;                     // which 32 query columns
+        const int wq = warp & 3;
+        const int r = wq * 32 + lane;                // key row inside the tile
+        const int kv_g = n * BKV + r;
+        const bool row_dead = kv_g >= T;
+        const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+        const float c = prm.scale_log2;
+
+        for (int it = 0; it < nblk; ++it) {
+            const int b = it & 1, s = it % NS, m = m0 + it;
+            const uint32_t par = (it >> 1) & 1;
+            const float* v_lse = sVec + s * 2 * BQ + h * 32;
+            const float* v_del = v_lse + BQ;
+            const uint32_t t_st = tmem + TR::TM_ST + b * 64 + h * 32 + lane_base;
+            const uint32_t t_dp = tmem + TR::TM_DP + b * 64 + h * 32 + lane_base;
+            mbar_wait(&qdo_full[s], (it / NS) & 1, ab, 30);      // lse / delta visible
+            mbar_wait(&st_full[b], par, ab, 31);
+            tc_fence_after_sync();
+            uint32_t sr[32];
+            tmem_ld_x32(t_st, sr);
+            tmem_wait_ld();
+            float p[32];
+            const bool diag = prm.causal && (m * BQ < (n + 1) * BKV);
+            const int q0 = m * BQ + h * 32;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                float x = fast_exp2(fmaf(__uint_as_float(sr[e]), c, -v_lse[e]));
+                if (row_dead || (diag && kv_g > q0 + e)) x = 0.f;
+                p[e] = x;
+            }
+            uint32_t pk[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) pk[e] = pack_bf16x2(p[2 * e], p[2 * e + 1]);
+            tmem_st_x16(t_st, pk);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[b]);
+
+            mbar_wait(&dp_full[b], par, ab, 32);
+            tc_fence_after_sync();
+            tmem_ld_x32(t_dp, sr);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                const float d0 = p[2 * e] * (__uint_as_float(sr[2 * e]) - v_del[2 * e]);
+                const float d1 = p[2 * e + 1] * (__uint_as_float(sr[2 * e + 1]) - v_del[2 * e + 1]);
+                pk[e] = pack_bf16x2(d0, d1);
+            }
+            tmem_st_x16(t_dp, pk);
+            uint8_t* ds_row = sDS + b * TR::DS_TILE;
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4)
+                *reinterpret_cast<uint4*>(ds_row + sw128_offset(r, h * 4 + c4)) = make_uint4(pk[4 * c4], pk[4 * c4 + 1], pk[4 * c4 + 2], pk[4 * c4 + 3]);
+            tmem_wait_st();
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ds_full[b]);
+        }
+
+        // ---- epilogue: warps 0-3 write dV, warps 4-7 write dK (scaled) ----
+        mbar_wait(dkv_full, 0, ab, 33);
+        tc_fence_after_sync();
+        {
+            const uint32_t t_acc = tmem + (h ? TR::TM_DK : TR::TM_DV) + lane_base;
+            const float mul = h ? prm.scale : 1.f;
+            uint8_t* stage = sQ + h * TR::KV_TILE;
+#pragma unroll
+            for (int cc = 0; cc < D; cc += 32) {
+                uint32_t rr[32];
+                tmem_ld_x32(t_acc + cc, rr);
+                tmem_wait_ld();
+                const int panel = cc / 64, chunk0 = (cc % 64) / 8;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    uint4 v;
+                    v.x = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 0]) * mul, __uint_as_float(rr[q4 * 8 + 1]) * mul);
+                    v.y = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 2]) * mul, __uint_as_float(rr[q4 * 8 + 3]) * mul);
+                    v.z = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 4]) * mul, __uint_as_float(rr[q4 * 8 + 5]) * mul);
+                    v.w = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 6]) * mul, __uint_as_float(rr[q4 * 8 + 7]) * mul);
+                    *reinterpret_cast<uint4*>(stage + panel * TR::KV_PANEL + sw128_offset(r, chunk0 + q4)) = v;
+                }
+            }
+            fence_proxy_async_smem();
+            asm volatile("bar.sync %0, 128;" ::"r"(1 + h) : "memory");
+            if ((tid & 127) == 0) {
+                for (int p = 0; p < TR::NP; ++p)
+                    tma_store_3d(h ? &tm_dk : &tm_dv, stage + p * TR::KV_PANEL, p * 64, n * BKV, bh);
+                tma_store_commit();
+                tma_store_wait_all();
+            }
+        }
+    } else if (warp < 12) {
+        // ------------------------------ drain dQ^T ------------------------------
+        const int wq = warp & 3;
+        const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+        // M = D rows of dQ^T: D=128 fills all lanes; D=64 uses lanes 0-15 of each quarter
+        const int d = (D == 128) ? (wq * 32 + lane) : (wq * 16 + lane);
+        const bool lane_ok = (D == 128) || (lane < 16);
+        for (int it = 0; it < nblk; ++it) {
+            const int b = it & 1, m = m0 + it;
+            mbar_wait(&dq_full[b], (it >> 1) & 1, ab, 40);
+            tc_fence_after_sync();
+            uint32_t r0[32], r1[32];
+            tmem_ld_x32(tmem + TR::TM_DP + b * 64 + lane_base, r0);
+            tmem_ld_x32(tmem + TR::TM_DP + b * 64 + 32 + lane_base, r1);
+            tmem_wait_ld();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&dq_empty[b]);
+            if (lane_ok) {
+                float* base = prm.dq_acc + (static_cast<size_t>(bh) * T + static_cast<size_t>(m) * BQ) * D + d;
+                const int rows = min(BQ, T - m * BQ);
+#pragma unroll
+                for (int e = 0; e < 32; ++e)
+                    if (e < rows) atomicAdd(base + static_cast<size_t>(e) * D, __uint_as_float(r0[e]));
+#pragma unroll
+                for (int e = 0; e < 32; ++e)
+                    if (32 + e < rows) atomicAdd(base + static_cast<size_t>(32 + e) * D, __uint_as_float(r1[e]));
+            }
+        }
+    }
+
+    // ------------------------------ tear-down ------------------------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag != 0) {
+        for (int it = 0; it < 64; ++it) __nanosleep(1000);
+    }
+    if (warp == 13) tmem_dealloc(tmem, TR::TM_COLS);
 }
+
+}  // namespace ib200
