@@ -70,15 +70,14 @@ int check_common(int B, int H, int T, int D, int dtype, int math_mode, int causa
     if (dtype == IB200_DTYPE_F32 && math_mode != IB200_MATH_TF32 && math_mode != IB200_MATH_3XTF32) return IB200_ERR_INVALID_ARGUMENT;
     if (dtype == IB200_DTYPE_BF16 && D != 64 && D != 128) return IB200_ERR_UNSUPPORTED;
     if (dtype == IB200_DTYPE_F32 && D != 64) return IB200_ERR_UNSUPPORTED;
-    if (dtype == IB200_DTYPE_F32 && math_mode == IB200_MATH_3XTF32) return IB200_ERR_UNSUPPORTED;
     if (static_cast<long>(B) * H > 65535L * 32768L) return IB200_ERR_UNSUPPORTED;
     return IB200_OK;
 }
 
-size_t fwd_ws_bytes(long N, bool f32) { return kHeaderBytes + (f32 ? 3 * round_up(N * 4, 256) : 0); }
+size_t fwd_ws_bytes(long N, bool f32) { return kHeaderBytes + (f32 ? 6 * round_up(N * 2, 256) : 0); }
 size_t bwd_ws_bytes(long N, long BH, int T, bool f32) {
     return kHeaderBytes + round_up(N * 4, 256) /*dq accumulator*/ + round_up(static_cast<size_t>(BH) * T * 4, 256) /*delta*/ +
-           (f32 ? 4 * round_up(N * 4, 256) : 0);
+           (f32 ? 8 * round_up(N * 2, 256) : 0);
 }
 
 int device_ok() {
@@ -90,13 +89,19 @@ int device_ok() {
 }
 
 template <class TR>
-int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int* status, long BH, int T,
-               float scale, int causal, cudaStream_t stream) {
-    CUtensorMap tq, tk, tv, to;
-    const bool f32 = TR::TF32;
-    if (!make_tmap(&tq, q, f32, TR::D, T, BH, 128) || !make_tmap(&tk, k, f32, TR::D, T, BH, 128) ||
-        !make_tmap(&tv, v, f32, TR::D, T, BH, 128) || !make_tmap(&to, o, f32, TR::D, T, BH, 128))
+int launch_fwd(const void* q, const void* q_lo, const void* k, const void* k_lo, const void* v, const void* v_lo, void* o,
+               float* lse, int* status, long BH, int T, float scale, int causal, cudaStream_t stream) {
+    CUtensorMap tq, tql, tk, tkl, tv, tvl, to;
+    if (!make_tmap(&tq, q, false, TR::D, T, BH, 128) || !make_tmap(&tk, k, false, TR::D, T, BH, 128) ||
+        !make_tmap(&tv, v, false, TR::D, T, BH, 128) || !make_tmap(&to, o, TR::SPLIT, TR::D, T, BH, 128))
         return IB200_ERR_CUDA;
+    if (TR::SPLIT) {
+        if (!make_tmap(&tql, q_lo, false, TR::D, T, BH, 128) || !make_tmap(&tkl, k_lo, false, TR::D, T, BH, 128) ||
+            !make_tmap(&tvl, v_lo, false, TR::D, T, BH, 128))
+            return IB200_ERR_CUDA;
+    } else {
+        tql = tq; tkl = tk; tvl = tv;
+    }
     if (!cuda_ok(cudaFuncSetAttribute(attn_fwd_kernel<TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::SMEM_BYTES)))
         return IB200_ERR_CUDA;
     FwdParams prm;
@@ -107,22 +112,24 @@ int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
     prm.causal = causal;
     prm.scale_log2 = scale * 1.4426950408889634f;
     const int pairs = (T + 255) / 256;
-    // grid.y is limited to 65535: fold the head index over y and z
-    dim3 grid(pairs, static_cast<unsigned>(BH), 1);
     if (BH > 65535) return IB200_ERR_UNSUPPORTED;
-    attn_fwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tk, tv, to, prm);
+    dim3 grid(pairs, static_cast<unsigned>(BH), 1);
+    attn_fwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tql, tk, tkl, tv, tvl, to, prm);
     return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
 }
 
-
 template <class TR>
-int launch_bwd(const void* q, const void* k, const void* v, const void* dO, const float* lse, const float* delta,
-               float* dq_acc, void* dk, void* dv, int* status, long BH, int T, float scale, int causal,
-               cudaStream_t stream) {
-    CUtensorMap tq, tk, tv, tdo, tdk, tdv;
-    if (!make_tmap(&tq, q, false, TR::D, T, BH, TR::BQ) || !make_tmap(&tdo, dO, false, TR::D, T, BH, TR::BQ) ||
-        !make_tmap(&tk, k, false, TR::D, T, BH, TR::BKV) || !make_tmap(&tv, v, false, TR::D, T, BH, TR::BKV) ||
-        !make_tmap(&tdk, dk, false, TR::D, T, BH, TR::BKV) || !make_tmap(&tdv, dv, false, TR::D, T, BH, TR::BKV))
+int launch_bwd(const void* const q[2], const void* const k[2], const void* const v[2], const void* const dO[2],
+               const float* lse, const float* delta, float* dq_acc, void* dk, void* dv, int* status, long BH, int T,
+               float scale, int causal, cudaStream_t stream) {
+    CUtensorMap tq[2], tk[2], tv[2], tdo[2], tdk, tdv;
+    for (int i = 0; i < (TR::SPLIT ? 2 : 1); ++i) {
+        if (!make_tmap(&tq[i], q[i], false, TR::D, T, BH, TR::BQ) || !make_tmap(&tdo[i], dO[i], false, TR::D, T, BH, TR::BQ) ||
+            !make_tmap(&tk[i], k[i], false, TR::D, T, BH, TR::BKV) || !make_tmap(&tv[i], v[i], false, TR::D, T, BH, TR::BKV))
+            return IB200_ERR_CUDA;
+    }
+    if (!TR::SPLIT) { tq[1] = tq[0]; tk[1] = tk[0]; tv[1] = tv[0]; tdo[1] = tdo[0]; }
+    if (!make_tmap(&tdk, dk, TR::SPLIT, TR::D, T, BH, TR::BKV) || !make_tmap(&tdv, dv, TR::SPLIT, TR::D, T, BH, TR::BKV))
         return IB200_ERR_CUDA;
     if (!cuda_ok(cudaFuncSetAttribute(attn_bwd_kernel<TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::SMEM_BYTES)))
         return IB200_ERR_CUDA;
@@ -138,27 +145,45 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dO, cons
     prm.scale_log2 = scale * 1.4426950408889634f;
     if (BH > 65535) return IB200_ERR_UNSUPPORTED;
     dim3 grid((T + TR::BKV - 1) / TR::BKV, static_cast<unsigned>(BH), 1);
-    attn_bwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdk, tdv, prm);
+    attn_bwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq[0], tq[1], tk[0], tk[1], tv[0], tv[1], tdo[0], tdo[1], tdk, tdv, prm);
     return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
 }
 
-// delta pre-pass -> main kernel -> dQ finish.  Workspace: [header | dq accumulator | delta | (fp32 only) operand copies].
+// delta pre-pass -> main kernel -> dQ finish.
+// Workspace: [header | dq accumulator | delta | (fp32 only) hi/lo bf16 copies of q, k, v, dO].
 int launch_bwd_all(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
                    void* dq, void* dk, void* dv, long BH, int T, int D, float scale, int causal, bool f32,
                    uint8_t* ws, cudaStream_t stream) {
     const long N = BH * T * D;
     int* status = reinterpret_cast<int*>(ws);
     float* dq_acc = reinterpret_cast<float*>(ws + kHeaderBytes);
-    float* delta = reinterpret_cast<float*>(ws + kHeaderBytes + round_up(N * 4, 256));
+    uint8_t* after_acc = ws + kHeaderBytes + round_up(N * 4, 256);
+    float* delta = reinterpret_cast<float*>(after_acc);
     if (!cuda_ok(cudaMemsetAsync(ws, 0, kHeaderBytes + round_up(N * 4, 256), stream))) return IB200_ERR_CUDA;
-    if (f32) return IB200_ERR_UNSUPPORTED;
     int rc;
+    if (f32) {
+        uint8_t* base = after_acc + round_up(static_cast<size_t>(BH) * T * 4, 256);
+        const size_t slab = round_up(N * 2, 256);
+        const void* part[8];
+        const float* src[4] = {static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v), static_cast<const float*>(dO)};
+        for (int i = 0; i < 4; ++i) {
+            part[2 * i] = base + (2 * i) * slab;
+            part[2 * i + 1] = base + (2 * i + 1) * slab;
+            rc = launch_split_bf16(src[i], const_cast<void*>(part[2 * i]), const_cast<void*>(part[2 * i + 1]), N, stream);
+            if (rc) return rc;
+        }
+        rc = launch_delta<64, true>(o, dO, delta, BH * T, stream); if (rc) return rc;
+        rc = launch_bwd<BwdTraits<64, true>>(&part[0], &part[2], &part[4], &part[6], lse, delta, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
+        if (rc) return rc;
+        return launch_dq_finish<true>(dq_acc, dq, scale, N, stream);
+    }
+    const void* qq[2] = {q, q}; const void* kk[2] = {k, k}; const void* vv[2] = {v, v}; const void* dd[2] = {dO, dO};
     if (D == 64) {
         rc = launch_delta<64, false>(o, dO, delta, BH * T, stream); if (rc) return rc;
-        rc = launch_bwd<BwdTraits<64>>(q, k, v, dO, lse, delta, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
+        rc = launch_bwd<BwdTraits<64, false>>(qq, kk, vv, dd, lse, delta, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
     } else {
         rc = launch_delta<128, false>(o, dO, delta, BH * T, stream); if (rc) return rc;
-        rc = launch_bwd<BwdTraits<128>>(q, k, v, dO, lse, delta, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
+        rc = launch_bwd<BwdTraits<128, false>>(qq, kk, vv, dd, lse, delta, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
     }
     if (rc) return rc;
     return launch_dq_finish<false>(dq_acc, dq, scale, N, stream);
@@ -218,18 +243,18 @@ int ib200_attn_fwd(const void* q, const void* k, const void* v, void* o, float* 
     int* status = reinterpret_cast<int*>(ws);
     if (!cuda_ok(cudaMemsetAsync(ws, 0, kHeaderBytes, stream))) return IB200_ERR_CUDA;
     if (f32) {
-        // operands rounded to TF32 (round-to-nearest) once, so the tensor core's truncation is exact
-        const size_t slab = round_up(N * 4, 256);
-        float* rq = reinterpret_cast<float*>(ws + kHeaderBytes);
-        float* rk = reinterpret_cast<float*>(ws + kHeaderBytes + slab);
-        float* rv = reinterpret_cast<float*>(ws + kHeaderBytes + 2 * slab);
-        rc = launch_round_tf32(static_cast<const float*>(q), rq, N, stream); if (rc) return rc;
-        rc = launch_round_tf32(static_cast<const float*>(k), rk, N, stream); if (rc) return rc;
-        rc = launch_round_tf32(static_cast<const float*>(v), rv, N, stream); if (rc) return rc;
-        return launch_fwd<FwdTraits<64, true>>(rq, rk, rv, o, lse, status, BH, T, scale, causal, stream);
+        // fp32 operands are carried as (hi, lo) bf16 pairs
+        const size_t slab = round_up(N * 2, 256);
+        uint8_t* base = ws + kHeaderBytes;
+        void* part[6];
+        for (int i = 0; i < 6; ++i) part[i] = base + i * slab;
+        rc = launch_split_bf16(static_cast<const float*>(q), part[0], part[1], N, stream); if (rc) return rc;
+        rc = launch_split_bf16(static_cast<const float*>(k), part[2], part[3], N, stream); if (rc) return rc;
+        rc = launch_split_bf16(static_cast<const float*>(v), part[4], part[5], N, stream); if (rc) return rc;
+        return launch_fwd<FwdTraits<64, true>>(part[0], part[1], part[2], part[3], part[4], part[5], o, lse, status, BH, T, scale, causal, stream);
     }
-    if (D == 64) return launch_fwd<FwdTraits<64, false>>(q, k, v, o, lse, status, BH, T, scale, causal, stream);
-    return launch_fwd<FwdTraits<128, false>>(q, k, v, o, lse, status, BH, T, scale, causal, stream);
+    if (D == 64) return launch_fwd<FwdTraits<64, false>>(q, q, k, k, v, v, o, lse, status, BH, T, scale, causal, stream);
+    return launch_fwd<FwdTraits<128, false>>(q, q, k, k, v, v, o, lse, status, BH, T, scale, causal, stream);
 }
 
 int ib200_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,

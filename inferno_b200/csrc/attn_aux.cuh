@@ -1,6 +1,6 @@
 // Bandwidth-bound helper kernels around the attention main kernels:
-//   * round_tf32   fp32 -> fp32 rounded to TF32 (round-to-nearest), so that the
-//                  tensor core's mantissa truncation of fp32 operands is exact
+//   * split_bf16   fp32 x -> (hi, lo) bf16 pair with hi = bf16(x), lo = bf16(x - hi); the
+//                  fp32-I/O kernels multiply such pairs in three bf16 MMAs
 //   * delta        delta[row] = sum_d O[row,d] * dO[row,d]; this is the reference's
 //                  dot = sum_j dP_ij P_ij (src/inferno/gradfn/softmaxbackward.h:101-109)
 //                  rewritten so that it needs no [T,T] matrix
@@ -18,22 +18,30 @@ namespace ib200 {
 constexpr int kAuxThreads = 256;
 constexpr int kAuxBlocks = 148 * 8;
 
-__global__ void __launch_bounds__(kAuxThreads) round_tf32_kernel(const float4* __restrict__ in, float4* __restrict__ out, long n4) {
-    for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n4; i += static_cast<long>(gridDim.x) * blockDim.x) {
-        float4 v = in[i];
-        uint32_t a, b, c, d;
-        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(a) : "f"(v.x));
-        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(b) : "f"(v.y));
-        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(c) : "f"(v.z));
-        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(d) : "f"(v.w));
-        out[i] = make_float4(__uint_as_float(a), __uint_as_float(b), __uint_as_float(c), __uint_as_float(d));
+// hi = bf16(x), lo = bf16(x - hi): 8 elements per thread, two 16-byte loads, two 16-byte stores.
+__global__ void __launch_bounds__(kAuxThreads) split_bf16_kernel(const float4* __restrict__ in, uint4* __restrict__ hi, uint4* __restrict__ lo, long n8) {
+    for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
+        const float4 a = in[2 * i], b = in[2 * i + 1];
+        const float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        uint32_t h[4], l[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const __nv_bfloat162 hh = __floats2bfloat162_rn(x[2 * e], x[2 * e + 1]);
+            const float2 hf = __bfloat1622float2(hh);
+            const __nv_bfloat162 ll = __floats2bfloat162_rn(x[2 * e] - hf.x, x[2 * e + 1] - hf.y);
+            h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+            l[e] = *reinterpret_cast<const uint32_t*>(&ll);
+        }
+        hi[i] = make_uint4(h[0], h[1], h[2], h[3]);
+        lo[i] = make_uint4(l[0], l[1], l[2], l[3]);
     }
 }
 
-inline int launch_round_tf32(const float* in, float* out, long n, cudaStream_t stream) {
-    const long n4 = n / 4;
-    const int blocks = static_cast<int>(n4 / kAuxThreads + 1 < kAuxBlocks ? n4 / kAuxThreads + 1 : kAuxBlocks);
-    round_tf32_kernel<<<blocks, kAuxThreads, 0, stream>>>(reinterpret_cast<const float4*>(in), reinterpret_cast<float4*>(out), n4);
+inline int launch_split_bf16(const float* in, void* hi, void* lo, long n, cudaStream_t stream) {
+    const long n8 = n / 8;
+    long blocks = n8 / kAuxThreads + 1;
+    if (blocks > kAuxBlocks) blocks = kAuxBlocks;
+    split_bf16_kernel<<<static_cast<int>(blocks), kAuxThreads, 0, stream>>>(reinterpret_cast<const float4*>(in), reinterpret_cast<uint4*>(hi), reinterpret_cast<uint4*>(lo), n8);
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 

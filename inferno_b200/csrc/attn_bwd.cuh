@@ -29,20 +29,30 @@
 #pragma once
 
 #include "attn_aux.cuh"
+#include "attn_fwd.cuh"
 #include "sm100_ptx.cuh"
 
 namespace ib200 {
 
-template <int D_>
+// SPLIT = true is the fp32-I/O mode for D = 64 (see FwdTraits): every operand tile is a
+// (hi, lo) bf16 pair occupying the two panels a D = 128 tile would, every product is three
+// MMAs, and P^T / dS^T are split into hi and lo parts as well.
+template <int D_, bool SPLIT_>
 struct BwdTraits {
     static constexpr int D = D_;
+    static constexpr bool SPLIT = SPLIT_;
+    static_assert(!SPLIT || D == 64, "split-bf16 mode is built for head dim 64");
     static constexpr int BKV = 128, BQ = 64;
-    static constexpr int NP = D * 2 / 128;                   // 128-byte column panels
+    static constexpr int NP = SPLIT ? 2 : D / 64;            // 128-byte panels per operand tile
     static constexpr int KV_PANEL = BKV * 128, KV_TILE = NP * KV_PANEL;
     static constexpr int Q_PANEL = BQ * 128, Q_TILE = NP * Q_PANEL;
-    static constexpr int DS_TILE = BKV * 128;                // [128 keys x 64 queries] bf16
-    static constexpr int NS = 3;                             // Q/dO ring depth
-    static constexpr int D_KSTEPS = D / 16;                  // k-steps over the head dim
+    static constexpr int DS_PART = BKV * 128;                // [128 keys x 64 queries] bf16
+    static constexpr int DS_TILE = (SPLIT ? 2 : 1) * DS_PART;
+    static constexpr int NS = SPLIT ? 2 : 3;                 // Q/dO ring depth
+    static constexpr int NTERMS = SPLIT ? 3 : 1;
+    static constexpr int OUT_TILE = SPLIT ? BKV * D * 4 : KV_TILE;   // dK / dV staging bytes
+    static constexpr int OUT_PANELS = SPLIT ? 2 : D / 64;
+    static constexpr int OUT_PANEL_ELEMS = SPLIT ? 32 : 64;
     static constexpr uint32_t IDESC_ST = make_idesc(kFmtBF16, BKV, BQ, kMajorK, kMajorK);
     static constexpr uint32_t IDESC_DKV = make_idesc(kFmtBF16, BKV, D, kMajorK, kMajorMN);
     static constexpr uint32_t IDESC_DQ = make_idesc(kFmtBF16, D, BQ, kMajorMN, kMajorMN);
@@ -56,7 +66,8 @@ struct BwdTraits {
     static constexpr int OFF_BAR = OFF_VEC + NS * 2 * BQ * 4;
     static constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
     static constexpr int THREADS = 512;
-    static_assert(2 * NS * Q_TILE >= 2 * KV_TILE, "epilogue staging must fit in the Q/dO ring");
+    static_assert(2 * NS * Q_TILE >= 2 * OUT_TILE, "epilogue staging must fit in the Q/dO ring");
+    static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
 struct BwdParams {
@@ -71,12 +82,70 @@ struct BwdParams {
 // TMEM column of the packed bf16 pair that starts k-step ks (16 queries) of P^T / dS^T:
 // queries 0-31 live in columns 0-15, queries 32-63 in columns 32-47 (each compute
 // warpgroup overwrites only the columns it has itself read).
-__device__ __forceinline__ uint32_t bwd_pcol(int ks) { return static_cast<uint32_t>((ks >> 1) * 32 + (ks & 1) * 8); }
+// In split mode the hi part takes the first 16 of a warpgroup's 32 columns and the lo part the next 16.
+__device__ __forceinline__ uint32_t bwd_pcol(int ks, int lo_part = 0) { return static_cast<uint32_t>((ks >> 1) * 32 + (ks & 1) * 8 + lo_part * 16); }
+
+// acc[128 keys x 64 queries] = A B^T with A = K or V tile, B = Q or dO block, both K-major (S^T and dP^T).
+template <class TR>
+__device__ __forceinline__ void bwd_issue_kmajor(uint32_t tmem_acc, uint32_t a_saddr, uint32_t b_saddr) {
+    if constexpr (!TR::SPLIT) {
+#pragma unroll
+        for (int k = 0; k < TR::D / 16; ++k)
+            umma_ss_f16(tmem_acc, make_sdesc_sw128(a_saddr + (k / 4) * TR::KV_PANEL + (k % 4) * 32, 16, 1024),
+                        make_sdesc_sw128(b_saddr + (k / 4) * TR::Q_PANEL + (k % 4) * 32, 16, 1024), TR::IDESC_ST, k > 0);
+    } else {
+#pragma unroll
+        for (int t = 0; t < 3; ++t)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                umma_ss_f16(tmem_acc, make_sdesc_sw128(a_saddr + split_a(t) * TR::KV_PANEL + k * 32, 16, 1024),
+                            make_sdesc_sw128(b_saddr + split_b(t) * TR::Q_PANEL + k * 32, 16, 1024), TR::IDESC_ST, (t | k) != 0);
+    }
+}
+
+// acc[128 keys x D] += A B with A = P^T or dS^T in TMEM (64 queries), B = dO or Q block, MN-major (dV and dK).
+template <class TR>
+__device__ __forceinline__ void bwd_issue_acc(uint32_t tmem_acc, uint32_t tmem_a, uint32_t b_saddr, bool accumulate) {
+    if constexpr (!TR::SPLIT) {
+#pragma unroll
+        for (int ks = 0; ks < TR::BQ / 16; ++ks)
+            umma_ts_f16(tmem_acc, tmem_a + bwd_pcol(ks), make_sdesc_sw128(b_saddr + ks * 2048, TR::Q_PANEL, 1024), TR::IDESC_DKV,
+                        (accumulate || ks > 0) ? 1u : 0u);
+    } else {
+#pragma unroll
+        for (int t = 0; t < 3; ++t)
+#pragma unroll
+            for (int ks = 0; ks < TR::BQ / 16; ++ks)
+                umma_ts_f16(tmem_acc, tmem_a + bwd_pcol(ks, split_a(t)),
+                            make_sdesc_sw128(b_saddr + split_b(t) * TR::Q_PANEL + ks * 2048, TR::Q_PANEL, 1024), TR::IDESC_DKV,
+                            (accumulate || (t | ks) != 0) ? 1u : 0u);
+    }
+}
+
+// acc[D x 64 queries] = K^T dS^T with K MN-major (M = head dim) and dS^T MN-major (N = queries).
+template <class TR>
+__device__ __forceinline__ void bwd_issue_dq(uint32_t tmem_acc, uint32_t k_saddr, uint32_t ds_saddr) {
+    if constexpr (!TR::SPLIT) {
+#pragma unroll
+        for (int ks = 0; ks < TR::BKV / 16; ++ks)
+            umma_ss_f16(tmem_acc, make_sdesc_sw128(k_saddr + ks * 2048, TR::KV_PANEL, 1024),
+                        make_sdesc_sw128(ds_saddr + ks * 2048, 16, 1024), TR::IDESC_DQ, ks > 0);
+    } else {
+#pragma unroll
+        for (int t = 0; t < 3; ++t)
+#pragma unroll
+            for (int ks = 0; ks < TR::BKV / 16; ++ks)
+                umma_ss_f16(tmem_acc, make_sdesc_sw128(k_saddr + split_a(t) * TR::KV_PANEL + ks * 2048, TR::KV_PANEL, 1024),
+                            make_sdesc_sw128(ds_saddr + split_b(t) * TR::DS_PART + ks * 2048, 16, 1024), TR::IDESC_DQ, (t | ks) != 0);
+    }
+}
 
 template <class TR>
 __global__ void __launch_bounds__(TR::THREADS, 1)
-attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_q_lo,
+                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_k_lo,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_v_lo,
+                const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_do_lo,
                 const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv, BwdParams prm) {
     constexpr int D = TR::D, BKV = TR::BKV, BQ = TR::BQ, NS = TR::NS;
     extern __shared__ uint8_t smem_raw[];
@@ -136,8 +205,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (lane == 0) {
             mbar_arrive_expect_tx(kv_full, 2 * TR::KV_TILE);
             for (int p = 0; p < TR::NP; ++p) {
-                tma_load_3d(sK + p * TR::KV_PANEL, &tm_k, kv_full, p * 64, n * BKV, bh);
-                tma_load_3d(sV + p * TR::KV_PANEL, &tm_v, kv_full, p * 64, n * BKV, bh);
+                const bool lo = TR::SPLIT && p;
+                tma_load_3d(sK + p * TR::KV_PANEL, lo ? &tm_k_lo : &tm_k, kv_full, TR::SPLIT ? 0 : p * 64, n * BKV, bh);
+                tma_load_3d(sV + p * TR::KV_PANEL, lo ? &tm_v_lo : &tm_v, kv_full, TR::SPLIT ? 0 : p * 64, n * BKV, bh);
             }
         }
         for (int it = 0; it < nblk; ++it) {
@@ -158,8 +228,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (lane == 0) {
                 mbar_arrive_expect_tx(&qdo_full[s], 2 * TR::Q_TILE);
                 for (int p = 0; p < TR::NP; ++p) {
-                    tma_load_3d(sQ + s * TR::Q_TILE + p * TR::Q_PANEL, &tm_q, &qdo_full[s], p * 64, m * BQ, bh);
-                    tma_load_3d(sDO + s * TR::Q_TILE + p * TR::Q_PANEL, &tm_do, &qdo_full[s], p * 64, m * BQ, bh);
+                    const bool lo = TR::SPLIT && p;
+                    tma_load_3d(sQ + s * TR::Q_TILE + p * TR::Q_PANEL, lo ? &tm_q_lo : &tm_q, &qdo_full[s], TR::SPLIT ? 0 : p * 64, m * BQ, bh);
+                    tma_load_3d(sDO + s * TR::Q_TILE + p * TR::Q_PANEL, lo ? &tm_do_lo : &tm_do, &qdo_full[s], TR::SPLIT ? 0 : p * 64, m * BQ, bh);
                 }
             }
         }
@@ -175,12 +246,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     mbar_wait(&qdo_full[s], (it / NS) & 1, ab, 21);
                     tc_fence_after_sync();
                     // S^T(it) = K Q^T
-#pragma unroll
-                    for (int k = 0; k < TR::D_KSTEPS; ++k) {
-                        const uint64_t ad = make_sdesc_sw128(aK + (k / 4) * TR::KV_PANEL + (k % 4) * 32, 16, 1024);
-                        const uint64_t bd = make_sdesc_sw128(aQ + (k / 4) * TR::Q_PANEL + (k % 4) * 32, 16, 1024);
-                        umma_ss_f16(tmem + TR::TM_ST + b * 64, ad, bd, TR::IDESC_ST, k > 0);
-                    }
+                    bwd_issue_kmajor<TR>(tmem + TR::TM_ST + b * 64, aK, aQ);
                     umma_commit(&st_full[b]);
                 }
                 const int j = it - 1, bj = j & 1, sj = j % NS;
@@ -189,40 +255,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     // dV += P^T(j) dO(j)
                     mbar_wait(&p_full[bj], (j >> 1) & 1, ab, 22);
                     tc_fence_after_sync();
-#pragma unroll
-                    for (int ks = 0; ks < BQ / 16; ++ks) {
-                        const uint64_t bd = make_sdesc_sw128(aDOj + ks * 2048, TR::Q_PANEL, 1024);
-                        umma_ts_f16(tmem + TR::TM_DV, tmem + TR::TM_ST + bj * 64 + bwd_pcol(ks), bd, TR::IDESC_DKV, (j > 0 || ks > 0) ? 1u : 0u);
-                    }
+                    bwd_issue_acc<TR>(tmem + TR::TM_DV, tmem + TR::TM_ST + bj * 64, aDOj, j > 0);
                     // dK += dS^T(j) Q(j)
                     mbar_wait(&ds_full[bj], (j >> 1) & 1, ab, 23);
                     tc_fence_after_sync();
-#pragma unroll
-                    for (int ks = 0; ks < BQ / 16; ++ks) {
-                        const uint64_t bd = make_sdesc_sw128(aQj + ks * 2048, TR::Q_PANEL, 1024);
-                        umma_ts_f16(tmem + TR::TM_DK, tmem + TR::TM_DP + bj * 64 + bwd_pcol(ks), bd, TR::IDESC_DKV, (j > 0 || ks > 0) ? 1u : 0u);
-                    }
+                    bwd_issue_acc<TR>(tmem + TR::TM_DK, tmem + TR::TM_DP + bj * 64, aQj, j > 0);
                 }
                 if (it < nblk) {
                     // dP^T(it) = V dO^T, into the buffer the drain of dQ^T(it-2) has released
                     if (it >= 2) { mbar_wait(&dq_empty[b], ((it - 2) >> 1) & 1, ab, 24); tc_fence_after_sync(); }
-#pragma unroll
-                    for (int k = 0; k < TR::D_KSTEPS; ++k) {
-                        const uint64_t ad = make_sdesc_sw128(aV + (k / 4) * TR::KV_PANEL + (k % 4) * 32, 16, 1024);
-                        const uint64_t bd = make_sdesc_sw128(aDO + (k / 4) * TR::Q_PANEL + (k % 4) * 32, 16, 1024);
-                        umma_ss_f16(tmem + TR::TM_DP + b * 64, ad, bd, TR::IDESC_ST, k > 0);
-                    }
+                    bwd_issue_kmajor<TR>(tmem + TR::TM_DP + b * 64, aV, aDO);
                     umma_commit(&dp_full[b]);
                 }
                 if (j >= 0) {
                     // dQ^T(j) = K^T dS^T(j), over the dS^T/dP^T buffer that dK(j) has just consumed
                     const uint32_t aDS = smem_u32(sDS + bj * TR::DS_TILE);
-#pragma unroll
-                    for (int ks = 0; ks < BKV / 16; ++ks) {
-                        const uint64_t ad = make_sdesc_sw128(aK + ks * 2048, TR::KV_PANEL, 1024);
-                        const uint64_t bd = make_sdesc_sw128(aDS + ks * 2048, 16, 1024);
-                        umma_ss_f16(tmem + TR::TM_DP + bj * 64, ad, bd, TR::IDESC_DQ, ks > 0);
-                    }
+                    bwd_issue_dq<TR>(tmem + TR::TM_DP + bj * 64, aK, aDS);
                     umma_commit(&dq_full[bj]);
                     umma_commit(&qdo_empty[sj]);
                 }
@@ -261,10 +309,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 if (row_dead || (diag && kv_g > q0 + e)) x = 0.f;
                 p[e] = x;
             }
-            uint32_t pk[16];
+            uint32_t pk[16], pl[16];
 #pragma unroll
-            for (int e = 0; e < 16; ++e) pk[e] = pack_bf16x2(p[2 * e], p[2 * e + 1]);
+            for (int e = 0; e < 16; ++e) {
+                pk[e] = pack_bf16x2(p[2 * e], p[2 * e + 1]);
+                if constexpr (TR::SPLIT)
+                    pl[e] = pack_bf16x2(p[2 * e] - __uint_as_float(pk[e] << 16), p[2 * e + 1] - __uint_as_float(pk[e] & 0xffff0000u));
+            }
             tmem_st_x16(t_st, pk);
+            if constexpr (TR::SPLIT) tmem_st_x16(t_st + 16, pl);
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
@@ -279,12 +332,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const float d0 = p[2 * e] * (__uint_as_float(sr[2 * e]) - v_del[2 * e]);
                 const float d1 = p[2 * e + 1] * (__uint_as_float(sr[2 * e + 1]) - v_del[2 * e + 1]);
                 pk[e] = pack_bf16x2(d0, d1);
+                if constexpr (TR::SPLIT)
+                    pl[e] = pack_bf16x2(d0 - __uint_as_float(pk[e] << 16), d1 - __uint_as_float(pk[e] & 0xffff0000u));
             }
             tmem_st_x16(t_dp, pk);
+            if constexpr (TR::SPLIT) tmem_st_x16(t_dp + 16, pl);
             uint8_t* ds_row = sDS + b * TR::DS_TILE;
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4)
+            for (int c4 = 0; c4 < 4; ++c4) {
                 *reinterpret_cast<uint4*>(ds_row + sw128_offset(r, h * 4 + c4)) = make_uint4(pk[4 * c4], pk[4 * c4 + 1], pk[4 * c4 + 2], pk[4 * c4 + 3]);
+                if constexpr (TR::SPLIT)
+                    *reinterpret_cast<uint4*>(ds_row + TR::DS_PART + sw128_offset(r, h * 4 + c4)) = make_uint4(pl[4 * c4], pl[4 * c4 + 1], pl[4 * c4 + 2], pl[4 * c4 + 3]);
+            }
             tmem_wait_st();
             fence_proxy_async_smem();
             tc_fence_before_sync();
@@ -298,28 +357,41 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         {
             const uint32_t t_acc = tmem + (h ? TR::TM_DK : TR::TM_DV) + lane_base;
             const float mul = h ? prm.scale : 1.f;
-            uint8_t* stage = sQ + h * TR::KV_TILE;
+            uint8_t* stage = sQ + h * TR::OUT_TILE;
 #pragma unroll
             for (int cc = 0; cc < D; cc += 32) {
                 uint32_t rr[32];
                 tmem_ld_x32(t_acc + cc, rr);
                 tmem_wait_ld();
-                const int panel = cc / 64, chunk0 = (cc % 64) / 8;
+                if constexpr (!TR::SPLIT) {
+                    const int panel = cc / 64, chunk0 = (cc % 64) / 8;
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    uint4 v;
-                    v.x = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 0]) * mul, __uint_as_float(rr[q4 * 8 + 1]) * mul);
-                    v.y = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 2]) * mul, __uint_as_float(rr[q4 * 8 + 3]) * mul);
-                    v.z = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 4]) * mul, __uint_as_float(rr[q4 * 8 + 5]) * mul);
-                    v.w = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 6]) * mul, __uint_as_float(rr[q4 * 8 + 7]) * mul);
-                    *reinterpret_cast<uint4*>(stage + panel * TR::KV_PANEL + sw128_offset(r, chunk0 + q4)) = v;
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 v;
+                        v.x = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 0]) * mul, __uint_as_float(rr[q4 * 8 + 1]) * mul);
+                        v.y = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 2]) * mul, __uint_as_float(rr[q4 * 8 + 3]) * mul);
+                        v.z = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 4]) * mul, __uint_as_float(rr[q4 * 8 + 5]) * mul);
+                        v.w = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 6]) * mul, __uint_as_float(rr[q4 * 8 + 7]) * mul);
+                        *reinterpret_cast<uint4*>(stage + panel * TR::KV_PANEL + sw128_offset(r, chunk0 + q4)) = v;
+                    }
+                } else {
+                    const int panel = cc / 32;     // 32 fp32 columns = one 128-byte panel row
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; ++q4) {
+                        uint4 v;
+                        v.x = __float_as_uint(__uint_as_float(rr[q4 * 4 + 0]) * mul);
+                        v.y = __float_as_uint(__uint_as_float(rr[q4 * 4 + 1]) * mul);
+                        v.z = __float_as_uint(__uint_as_float(rr[q4 * 4 + 2]) * mul);
+                        v.w = __float_as_uint(__uint_as_float(rr[q4 * 4 + 3]) * mul);
+                        *reinterpret_cast<uint4*>(stage + panel * TR::KV_PANEL + sw128_offset(r, q4)) = v;
+                    }
                 }
             }
             fence_proxy_async_smem();
             asm volatile("bar.sync %0, 128;" ::"r"(1 + h) : "memory");
             if ((tid & 127) == 0) {
-                for (int p = 0; p < TR::NP; ++p)
-                    tma_store_3d(h ? &tm_dk : &tm_dv, stage + p * TR::KV_PANEL, p * 64, n * BKV, bh);
+                for (int p = 0; p < TR::OUT_PANELS; ++p)
+                    tma_store_3d(h ? &tm_dk : &tm_dv, stage + p * TR::KV_PANEL, p * TR::OUT_PANEL_ELEMS, n * BKV, bh);
                 tma_store_commit();
                 tma_store_wait_all();
             }

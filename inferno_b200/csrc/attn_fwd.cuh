@@ -26,29 +26,31 @@
 
 namespace ib200 {
 
-template <int D_, bool TF32_>
+// SPLIT = false: bf16 operands and output, head dim D (64 or 128).
+// SPLIT = true : fp32 I/O for D = 64.  Every fp32 operand x is carried as two bf16 tensors,
+//   x_hi = bf16(x) and x_lo = bf16(x - x_hi); a product a*b is evaluated as
+//   a_hi*b_hi + a_lo*b_hi + a_hi*b_lo on the bf16 tensor pipe with fp32 accumulation
+//   (relative error ~2^-16 per product, below a single TF32 pass at 2^-11).  The hi and
+//   lo tiles take the place of the two 64-column panels of a D = 128 tile, so the shared
+//   memory and TMEM budgets are those of the bf16 D = 128 kernel.
+template <int D_, bool SPLIT_>
 struct FwdTraits {
     static constexpr int D = D_;
-    static constexpr bool TF32 = TF32_;
-    static constexpr int ES = TF32 ? 4 : 2;                 // operand element size
-    static constexpr int OUT_ES = TF32 ? 4 : 2;             // output element size
+    static constexpr bool SPLIT = SPLIT_;
+    static_assert(!SPLIT || D == 64, "split-bf16 mode is built for head dim 64");
     static constexpr int BM = 128, BN = 128;                // query / key tile rows
-    static constexpr int PANEL_ELEMS = 128 / ES;            // elements per 128-byte swizzle row
-    static constexpr int NP = D * ES / 128;                 // 128-byte column panels per tile
+    static constexpr int NP = SPLIT ? 2 : D / 64;           // 128-byte panels per operand tile (hi/lo or column halves)
     static constexpr int PANEL_BYTES = 128 * 128;           // [128 rows x 128 B]
     static constexpr int TILE_BYTES = NP * PANEL_BYTES;
-    static constexpr int UMMA_K = 32 / ES;                  // elements per MMA k-step
-    static constexpr int S_KSTEPS = D / UMMA_K;             // k-steps of Q K^T
-    static constexpr int KSTEPS_PER_PANEL = 4;              // 128 B / 32 B
-    static constexpr int PV_KSTEPS = BN / UMMA_K;           // k-steps of P V
-    static constexpr int PV_KSTEP_BYTES = UMMA_K * 128;     // UMMA_K key rows of 128 B
-    static constexpr int P_COLS = BN * ES / 4;              // TMEM columns holding P
+    static constexpr int NTERMS = SPLIT ? 3 : 1;
+    static constexpr int PV_KSTEPS = BN / 16;               // k-steps of P V (16 keys each)
     static constexpr int KV_STAGES = (TILE_BYTES <= 16384) ? 4 : 2;
-    static constexpr uint32_t FMT = TF32 ? kFmtTF32 : kFmtBF16;
-    static constexpr uint32_t IDESC_S = make_idesc(FMT, BM, BN, kMajorK, kMajorK);
-    static constexpr uint32_t IDESC_PV = make_idesc(FMT, BM, D, kMajorK, kMajorMN);
+    static constexpr uint32_t IDESC_S = make_idesc(kFmtBF16, BM, BN, kMajorK, kMajorK);
+    static constexpr uint32_t IDESC_PV = make_idesc(kFmtBF16, BM, D, kMajorK, kMajorMN);
     // TMEM columns: S0, S1 (128 each), O0, O1 (D each, padded to 128)
     static constexpr uint32_t TM_S0 = 0, TM_S1 = 128, TM_O0 = 256, TM_O1 = 384, TM_COLS = 512;
+    static constexpr int OUT_PANELS = SPLIT ? 2 : D / 64;   // output staging panels ([128 x 128 B] each)
+    static constexpr int OUT_PANEL_ELEMS = SPLIT ? 32 : 64;
     static constexpr int SMEM_TILES = 2 + 2 * KV_STAGES;
     static constexpr int SMEM_BYTES = SMEM_TILES * TILE_BYTES + 1024 /*align slack*/ + 512 /*barriers*/;
     static constexpr int THREADS = 384;                      // 3 warpgroups: softmax 0, softmax 1, {MMA, TMA, 2 idle}
@@ -64,33 +66,53 @@ struct FwdParams {
 
 constexpr float kRescaleLog2 = 8.0f;
 
+// Operand panel used by term t of a split product: a_hi*b_hi, a_lo*b_hi, a_hi*b_lo.
+__device__ __forceinline__ constexpr int split_a(int t) { return t == 1 ? 1 : 0; }
+__device__ __forceinline__ constexpr int split_b(int t) { return t == 2 ? 1 : 0; }
+
 template <class TR>
 __device__ __forceinline__ void fwd_issue_s(uint32_t tmem_s, uint32_t q_saddr, uint32_t k_saddr) {
+    if constexpr (!TR::SPLIT) {
 #pragma unroll
-    for (int k = 0; k < TR::S_KSTEPS; ++k) {
-        const uint32_t off = (k / TR::KSTEPS_PER_PANEL) * TR::PANEL_BYTES + (k % TR::KSTEPS_PER_PANEL) * 32;
-        const uint64_t ad = make_sdesc_sw128(q_saddr + off, 16, 1024);
-        const uint64_t bd = make_sdesc_sw128(k_saddr + off, 16, 1024);
-        if constexpr (TR::TF32) umma_ss_tf32(tmem_s, ad, bd, TR::IDESC_S, k > 0);
-        else umma_ss_f16(tmem_s, ad, bd, TR::IDESC_S, k > 0);
+        for (int k = 0; k < TR::D / 16; ++k) {
+            const uint32_t off = (k / 4) * TR::PANEL_BYTES + (k % 4) * 32;
+            umma_ss_f16(tmem_s, make_sdesc_sw128(q_saddr + off, 16, 1024), make_sdesc_sw128(k_saddr + off, 16, 1024), TR::IDESC_S, k > 0);
+        }
+    } else {
+#pragma unroll
+        for (int t = 0; t < 3; ++t)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                umma_ss_f16(tmem_s, make_sdesc_sw128(q_saddr + split_a(t) * TR::PANEL_BYTES + k * 32, 16, 1024),
+                            make_sdesc_sw128(k_saddr + split_b(t) * TR::PANEL_BYTES + k * 32, 16, 1024), TR::IDESC_S, (t | k) != 0);
     }
 }
 
 template <class TR>
 __device__ __forceinline__ void fwd_issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t v_saddr, bool first_tile) {
+    if constexpr (!TR::SPLIT) {
 #pragma unroll
-    for (int k = 0; k < TR::PV_KSTEPS; ++k) {
-        const uint64_t bd = make_sdesc_sw128(v_saddr + k * TR::PV_KSTEP_BYTES, TR::PANEL_BYTES, 1024);
-        const uint32_t acc = (!first_tile || k > 0) ? 1u : 0u;
-        if constexpr (TR::TF32) umma_ts_tf32(tmem_o, tmem_p + k * 8, bd, TR::IDESC_PV, acc);
-        else umma_ts_f16(tmem_o, tmem_p + k * 8, bd, TR::IDESC_PV, acc);
+        for (int k = 0; k < TR::PV_KSTEPS; ++k)
+            umma_ts_f16(tmem_o, tmem_p + k * 8, make_sdesc_sw128(v_saddr + k * 2048, TR::PANEL_BYTES, 1024), TR::IDESC_PV,
+                        (!first_tile || k > 0) ? 1u : 0u);
+    } else {
+        // P_hi in columns 0-63, P_lo in columns 64-127 of the S region; V_hi / V_lo are the two panels
+#pragma unroll
+        for (int t = 0; t < 3; ++t)
+#pragma unroll
+            for (int k = 0; k < TR::PV_KSTEPS; ++k)
+                umma_ts_f16(tmem_o, tmem_p + split_a(t) * 64 + k * 8,
+                            make_sdesc_sw128(v_saddr + split_b(t) * TR::PANEL_BYTES + k * 2048, TR::PANEL_BYTES, 1024), TR::IDESC_PV,
+                            (!first_tile || (t | k) != 0) ? 1u : 0u);
     }
 }
 
 template <class TR>
 __global__ void __launch_bounds__(TR::THREADS, 1)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, FwdParams prm) {
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_q_lo,
+                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_k_lo,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_v_lo,
+                const __grid_constant__ CUtensorMap tm_o, FwdParams prm) {
     constexpr int D = TR::D, BM = TR::BM, BN = TR::BN, KS = TR::KV_STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -132,7 +154,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         fence_mbar_init();
     }
     if (warp == 8) { tmem_alloc(tmem_slot, TR::TM_COLS); tmem_relinquish(); }
-    if (warp == 9 && lane == 0) { tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_o); }
+    if (warp == 9 && lane == 0) { tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_o);
+        if constexpr (TR::SPLIT) { tma_prefetch_desc(&tm_q_lo); tma_prefetch_desc(&tm_k_lo); tma_prefetch_desc(&tm_v_lo); } }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -149,18 +172,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mbar_arrive_expect_tx(q_full, q_tiles * TR::TILE_BYTES);
             for (int i = 0; i < q_tiles; ++i)
                 for (int p = 0; p < TR::NP; ++p)
-                    tma_load_3d(sQ + i * TR::TILE_BYTES + p * TR::PANEL_BYTES, &tm_q, q_full, p * TR::PANEL_ELEMS, m_tile[i] * BM, bh);
+                    tma_load_3d(sQ + i * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_q_lo : &tm_q, q_full, TR::SPLIT ? 0 : p * 64, m_tile[i] * BM, bh);
             for (int j = 0; j < n_iter; ++j) {
                 const int s = j % KS;
                 const uint32_t ph = (j / KS) & 1;
                 mbar_wait(&k_empty[s], ph ^ 1, ab, 10);
                 mbar_arrive_expect_tx(&k_full[s], TR::TILE_BYTES);
                 for (int p = 0; p < TR::NP; ++p)
-                    tma_load_3d(sK + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, &tm_k, &k_full[s], p * TR::PANEL_ELEMS, j * BN, bh);
+                    tma_load_3d(sK + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_k_lo : &tm_k, &k_full[s], TR::SPLIT ? 0 : p * 64, j * BN, bh);
                 mbar_wait(&v_empty[s], ph ^ 1, ab, 11);
                 mbar_arrive_expect_tx(&v_full[s], TR::TILE_BYTES);
                 for (int p = 0; p < TR::NP; ++p)
-                    tma_load_3d(sV + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, &tm_v, &v_full[s], p * TR::PANEL_ELEMS, j * BN, bh);
+                    tma_load_3d(sV + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_v_lo : &tm_v, &v_full[s], TR::SPLIT ? 0 : p * 64, j * BN, bh);
             }
         }
     } else if (warp == 8) {
@@ -260,33 +283,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 }
             }
             float lsum = 0.f;
-            if constexpr (!TR::TF32) {
 #pragma unroll
-                for (int cc = 0; cc < BN; cc += 32) {
-                    uint32_t pk[16];
+            for (int cc = 0; cc < BN; cc += 32) {
+                uint32_t pk[16], pl[16];
 #pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
-                        const float p0 = fast_exp2(fmaf(s[cc + e], c, -m_used));
-                        const float p1 = fast_exp2(fmaf(s[cc + e + 1], c, -m_used));
-                        lsum += p0 + p1;
-                        pk[e >> 1] = pack_bf16x2(p0, p1);
-                    }
-                    tmem_st_x16(tm_s + (cc >> 1), pk);
+                for (int e = 0; e < 32; e += 2) {
+                    const float p0 = fast_exp2(fmaf(s[cc + e], c, -m_used));
+                    const float p1 = fast_exp2(fmaf(s[cc + e + 1], c, -m_used));
+                    lsum += p0 + p1;
+                    const uint32_t hi = pack_bf16x2(p0, p1);
+                    pk[e >> 1] = hi;
+                    if constexpr (TR::SPLIT)
+                        pl[e >> 1] = pack_bf16x2(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xffff0000u));
                 }
-            } else {
-#pragma unroll
-                for (int cc = 0; cc < BN; cc += 32) {
-                    uint32_t pk[32];
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const float p0 = fast_exp2(fmaf(s[cc + e], c, -m_used));
-                        lsum += p0;
-                        uint32_t u;
-                        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(p0));
-                        pk[e] = u;
-                    }
-                    tmem_st_x32(tm_s + cc, pk);
-                }
+                tmem_st_x16(tm_s + (cc >> 1), pk);
+                if constexpr (TR::SPLIT) tmem_st_x16(tm_s + 64 + (cc >> 1), pl);
             }
             l += lsum;
             tmem_wait_st();
@@ -305,7 +316,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 uint32_t r[32];
                 tmem_ld_x32(tm_oo + cc, r);
                 tmem_wait_ld();
-                if constexpr (!TR::TF32) {
+                if constexpr (!TR::SPLIT) {
                     // 32 columns = 64 bytes = 4 chunks of 16 B inside panel cc/64
                     const int panel = cc / 64, chunk0 = (cc % 64) / 8;
 #pragma unroll
@@ -335,8 +346,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             fence_proxy_async_smem();
             asm volatile("bar.sync %0, 128;" ::"r"(1 + i) : "memory");
             if (t == 0) {
-                for (int p = 0; p < TR::NP; ++p)
-                    tma_store_3d(&tm_o, stage + p * TR::PANEL_BYTES, p * TR::PANEL_ELEMS, m_tile[i] * BM, bh);
+                for (int p = 0; p < TR::OUT_PANELS; ++p)
+                    tma_store_3d(&tm_o, stage + p * TR::PANEL_BYTES, p * TR::OUT_PANEL_ELEMS, m_tile[i] * BM, bh);
                 tma_store_commit();
                 tma_store_wait_all();
             }
