@@ -80,6 +80,15 @@ int ib200_attn_bwd(const void* q, const void* k, const void* v, const void* o, c
  * (src/inferno/cuda/cudaops.h:198-210); this library reports instead of exiting. */
 int ib200_attn_check(const void* workspace, ib200_stream_t stream, int* device_code);
 
+/* Observability hook: CUDA events (cudaEvent_t handles, or NULL) that the following calls on this
+ * host thread record on their stream immediately before and after the forward main kernel and the
+ * backward main kernel, so a caller can time those kernels apart from the helper passes around
+ * them.  Pass four NULLs to switch it off (the default).  The reference's counterpart is its
+ * wall-clock lap timer around ops (InfernoApp/timer.h:10-40, laps at InfernoApp/main.cpp:713-765). */
+typedef struct CUevent_st* ib200_event_t;
+int ib200_attn_set_timing_events(ib200_event_t fwd_start, ib200_event_t fwd_stop,
+                                 ib200_event_t bwd_start, ib200_event_t bwd_stop);
+
 /* Human-readable name of a status value; never NULL. */
 const char* ib200_status_string(int status);
 

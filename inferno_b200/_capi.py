@@ -18,7 +18,7 @@ PASS_FWD, PASS_BWD = 0, 1
 
 EXPORTS = (
     "ib200_attn_workspace_bytes", "ib200_attn_fwd", "ib200_attn_bwd", "ib200_attn_check",
-    "ib200_status_string", "ib200_last_cuda_error", "ib200_version",
+    "ib200_status_string", "ib200_last_cuda_error", "ib200_version", "ib200_attn_set_timing_events",
 )
 
 _lib = None
@@ -47,6 +47,8 @@ def lib() -> ctypes.CDLL:
         L.ib200_attn_bwd.restype = i
         L.ib200_attn_check.argtypes = [vp, vp, ctypes.POINTER(i)]
         L.ib200_attn_check.restype = i
+        L.ib200_attn_set_timing_events.argtypes = [vp, vp, vp, vp]
+        L.ib200_attn_set_timing_events.restype = i
         L.ib200_status_string.argtypes = [i]
         L.ib200_status_string.restype = ctypes.c_char_p
         L.ib200_last_cuda_error.restype = i

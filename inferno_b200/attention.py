@@ -121,6 +121,20 @@ def check_device_status(device=None) -> None:
         raise _capi.Ib200Error(rc, f"ib200_attn_check (device code {code.value})")
 
 
+def set_timing_events(fwd_start=None, fwd_stop=None, bwd_start=None, bwd_stop=None) -> None:
+    """Have later calls on this thread record these ``torch.cuda.Event``s (timing enabled, created on the
+    current device) right around the forward / backward main kernels.  No arguments switches it off."""
+    handles = []
+    for ev in (fwd_start, fwd_stop, bwd_start, bwd_stop):
+        if ev is None:
+            handles.append(None)
+        else:
+            if not ev.cuda_event:          # torch creates the event lazily, on first record
+                ev.record()
+            handles.append(ev.cuda_event)
+    _raise(_capi.lib().ib200_attn_set_timing_events(*handles), "ib200_attn_set_timing_events")
+
+
 class AttentionBackward(torch.autograd.Function):
     """The backward node of the fused op: saves q, k, v, out and lse; produces dq, dk, dv.
 

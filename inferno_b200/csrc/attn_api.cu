@@ -15,6 +15,7 @@ namespace {
 using namespace ib200;
 
 thread_local int g_last_cuda_error = 0;
+thread_local cudaEvent_t g_ev[4] = {nullptr, nullptr, nullptr, nullptr};   // fwd start/stop, bwd start/stop
 
 inline bool cuda_ok(cudaError_t e) {
     if (e == cudaSuccess) return true;
@@ -114,7 +115,9 @@ int launch_fwd(const void* q, const void* q_lo, const void* k, const void* k_lo,
     const int pairs = (T + 255) / 256;
     if (BH > 65535) return IB200_ERR_UNSUPPORTED;
     dim3 grid(pairs, static_cast<unsigned>(BH), 1);
+    if (g_ev[0]) cudaEventRecord(g_ev[0], stream);
     attn_fwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tql, tk, tkl, tv, tvl, to, prm);
+    if (g_ev[1]) cudaEventRecord(g_ev[1], stream);
     return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
 }
 
@@ -145,7 +148,9 @@ int launch_bwd(const void* const q[2], const void* const k[2], const void* const
     prm.scale_log2 = scale * 1.4426950408889634f;
     if (BH > 65535) return IB200_ERR_UNSUPPORTED;
     dim3 grid((T + TR::BKV - 1) / TR::BKV, static_cast<unsigned>(BH), 1);
+    if (g_ev[2]) cudaEventRecord(g_ev[2], stream);
     attn_bwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq[0], tq[1], tk[0], tk[1], tv[0], tv[1], tdo[0], tdo[1], tdk, tdv, prm);
+    if (g_ev[3]) cudaEventRecord(g_ev[3], stream);
     return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
 }
 
@@ -196,6 +201,14 @@ extern "C" {
 int ib200_version(void) { return 1000; }
 
 int ib200_last_cuda_error(void) { return g_last_cuda_error; }
+
+int ib200_attn_set_timing_events(ib200_event_t fwd_start, ib200_event_t fwd_stop, ib200_event_t bwd_start, ib200_event_t bwd_stop) {
+    g_ev[0] = reinterpret_cast<cudaEvent_t>(fwd_start);
+    g_ev[1] = reinterpret_cast<cudaEvent_t>(fwd_stop);
+    g_ev[2] = reinterpret_cast<cudaEvent_t>(bwd_start);
+    g_ev[3] = reinterpret_cast<cudaEvent_t>(bwd_stop);
+    return IB200_OK;
+}
 
 const char* ib200_status_string(int status) {
     switch (status) {

@@ -1,0 +1,121 @@
+"""The C-ABI library: it loads, exports what the header declares, and validates arguments on the host.
+
+No compute call is made here (there is no GPU); with valid arguments and no device the entry
+points must fail loudly with IB200_ERR_NO_DEVICE rather than fall back to anything.
+"""
+import ctypes
+import os
+import re
+
+import pytest
+
+from inferno_b200 import _capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = set()
+    inc = os.path.join(ROOT, "include")
+    for fn in os.listdir(inc):
+        if fn.endswith(".h"):
+            text = open(os.path.join(inc, fn)).read()
+            text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+            names.update(re.findall(r"\b(ib200_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    lib = ctypes.CDLL(built_lib)
+    syms = declared_symbols()
+    assert "ib200_attn_fwd" in syms and "ib200_attn_bwd" in syms and len(syms) >= 7
+    for name in syms:
+        assert hasattr(lib, name), f"{name} is declared in include/ but not exported"
+
+
+def test_binding_lists_match_header(built_lib):
+    assert set(_capi.EXPORTS) <= set(declared_symbols())
+    assert _capi.lib().ib200_version() >= 1000
+
+
+def test_status_strings(built_lib):
+    seen = set()
+    for code in range(0, 8):
+        s = _capi.status_string(code)
+        assert s and s != "unknown status"
+        seen.add(s)
+    assert len(seen) == 8
+    assert _capi.status_string(999) == "unknown status"
+
+
+def test_workspace_query(built_lib):
+    # bf16 forward needs only the status header; backward adds the fp32 dQ accumulator and delta
+    assert _capi.workspace_bytes(2, 3, 100, 64, _capi.DTYPE_BF16, _capi.PASS_FWD) == 256
+    n = 2 * 3 * 100 * 64
+    bwd = _capi.workspace_bytes(2, 3, 100, 64, _capi.DTYPE_BF16, _capi.PASS_BWD)
+    assert bwd >= 256 + 4 * n + 4 * 2 * 3 * 100
+    # fp32 I/O carries hi/lo bf16 copies of the operands
+    assert _capi.workspace_bytes(2, 3, 100, 64, _capi.DTYPE_F32, _capi.PASS_FWD) >= 256 + 6 * 2 * n
+    assert _capi.workspace_bytes(2, 3, 100, 64, _capi.DTYPE_F32, _capi.PASS_BWD) >= bwd + 8 * 2 * n
+    out = ctypes.c_size_t(0)
+    L = _capi.lib()
+    assert L.ib200_attn_workspace_bytes(1, 1, 16, 96, _capi.DTYPE_BF16, 0, ctypes.byref(out)) == _capi.ERR_UNSUPPORTED
+    assert L.ib200_attn_workspace_bytes(1, 1, 16, 128, _capi.DTYPE_F32, 0, ctypes.byref(out)) == _capi.ERR_UNSUPPORTED
+    assert L.ib200_attn_workspace_bytes(0, 1, 16, 64, _capi.DTYPE_BF16, 0, ctypes.byref(out)) == _capi.ERR_INVALID_ARGUMENT
+    assert L.ib200_attn_workspace_bytes(1, 1, 16, 64, 7, 0, ctypes.byref(out)) == _capi.ERR_INVALID_ARGUMENT
+    assert L.ib200_attn_workspace_bytes(1, 1, 16, 64, _capi.DTYPE_BF16, 2, ctypes.byref(out)) == _capi.ERR_INVALID_ARGUMENT
+    assert L.ib200_attn_workspace_bytes(1, 1, 16, 64, _capi.DTYPE_BF16, 0, None) == _capi.ERR_INVALID_ARGUMENT
+
+
+def _fwd(L, ptrs, B=1, H=1, T=16, D=64, scale=0.125, causal=1, dtype=_capi.DTYPE_BF16, ws=0x1000, ws_bytes=1 << 20):
+    q, k, v, o, lse = ptrs
+    return L.ib200_attn_fwd(q, k, v, o, lse, B, H, T, D, scale, causal, dtype, 0, ws, ws_bytes, None)
+
+
+def test_forward_argument_validation(built_lib):
+    """Host-side rejection happens before any CUDA call; fake (never dereferenced) addresses suffice."""
+    L = _capi.lib()
+    good = (0x10000, 0x20000, 0x30000, 0x40000, 0x50000)
+    assert _fwd(L, (None,) + good[1:]) == _capi.ERR_INVALID_ARGUMENT
+    assert _fwd(L, good, T=0) == _capi.ERR_INVALID_ARGUMENT
+    assert _fwd(L, good, causal=2) == _capi.ERR_INVALID_ARGUMENT
+    assert _fwd(L, good, scale=0.0) == _capi.ERR_INVALID_ARGUMENT
+    assert _fwd(L, good, scale=float("nan")) == _capi.ERR_INVALID_ARGUMENT
+    assert _fwd(L, good, D=80) == _capi.ERR_UNSUPPORTED
+    assert _fwd(L, (0x10004,) + good[1:]) == _capi.ERR_MISALIGNED
+    assert _fwd(L, good, ws=None) == _capi.ERR_WORKSPACE
+    assert _fwd(L, good, ws_bytes=16) == _capi.ERR_WORKSPACE
+
+
+def test_backward_argument_validation(built_lib):
+    L = _capi.lib()
+    p = [0x10000 * (i + 1) for i in range(9)]
+
+    def bwd(ptrs, T=16, D=64, ws=0x1000, ws_bytes=1 << 20, dtype=_capi.DTYPE_BF16):
+        return L.ib200_attn_bwd(*ptrs, 1, 1, T, D, 0.125, 1, dtype, 0, ws, ws_bytes, None)
+
+    assert bwd([None] + p[1:]) == _capi.ERR_INVALID_ARGUMENT
+    assert bwd(p[:8] + [None]) == _capi.ERR_INVALID_ARGUMENT
+    assert bwd(p, D=32) == _capi.ERR_UNSUPPORTED
+    assert bwd(p[:6] + [p[6] + 8] + p[7:]) == _capi.ERR_MISALIGNED
+    assert bwd(p, ws_bytes=256) == _capi.ERR_WORKSPACE
+
+
+def test_no_device_fails_loudly(built_lib):
+    """With well-formed arguments and no sm_100 device the call reports it; nothing else runs."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    L = _capi.lib()
+    good = (0x10000, 0x20000, 0x30000, 0x40000, 0x50000)
+    assert _fwd(L, good) == _capi.ERR_NO_DEVICE
+
+
+def test_python_host_side_rejects_cpu_tensors(built_lib):
+    import torch
+    from inferno_b200 import attention as A
+    q = torch.zeros(1, 1, 16, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        A.attention_forward(q, q, q)
+    with pytest.raises(ValueError):
+        A.attention_forward(q[0], q[0], q[0])
