@@ -21,6 +21,14 @@
 // dQ^T leaves through coalesced fp32 reductions into a scratch accumulator
 // (lane = head-dim index, so a warp adds 32 consecutive floats per instruction).
 //
+// Software pipeline of the MMA issuer (block = one 64-row query block, b = block & 1):
+//   prologue   S^T(0) dP^T(0) S^T(1) dP^T(1)
+//   phase it   dQ^T(it) dK(it) dV(it) | S^T(it+2) dP^T(it+2)
+// so the compute warps work on block it+1 while the tensor pipe runs phase it, and the
+// drain of dQ^T(it) has three MMAs of slack before dP^T(it+2) reuses its TMEM buffer.
+// P^T and dS^T (bf16) both live in the S^T buffer, so dQ^T may overwrite the dP^T
+// buffer as soon as the compute warps have read it.
+//
 //   warps 0-7    compute: P^T = exp2(S^T c - lse), dS^T = P^T (dP^T - delta); each
 //                thread owns one key row; warps 0-3 take query columns 0-31, 4-7 take 32-63
 //   warps 8-11   drain dQ^T from TMEM to the global accumulator
@@ -48,7 +56,7 @@ struct BwdTraits {
     static constexpr int Q_PANEL = BQ * 128, Q_TILE = NP * Q_PANEL;
     static constexpr int DS_PART = BKV * 128;                // [128 keys x 64 queries] bf16
     static constexpr int DS_TILE = (SPLIT ? 2 : 1) * DS_PART;
-    static constexpr int NS = SPLIT ? 2 : 3;                 // Q/dO ring depth
+    static constexpr int NS = SPLIT ? 3 : 4;                 // Q/dO ring depth
     static constexpr int NTERMS = SPLIT ? 3 : 1;
     static constexpr int OUT_TILE = SPLIT ? BKV * D * 4 : KV_TILE;   // dK / dV staging bytes
     static constexpr int OUT_PANELS = SPLIT ? 2 : D / 64;
@@ -61,8 +69,8 @@ struct BwdTraits {
     static constexpr int OFF_V = OFF_K + KV_TILE;
     static constexpr int OFF_Q = OFF_V + KV_TILE;            // NS tiles; ring start, reused as dV/dK staging
     static constexpr int OFF_DO = OFF_Q + NS * Q_TILE;       // NS tiles
-    static constexpr int OFF_DS = OFF_DO + NS * Q_TILE;      // 2 tiles
-    static constexpr int OFF_VEC = OFF_DS + 2 * DS_TILE;     // NS x (lse[64], delta[64]) floats
+    static constexpr int OFF_DS = OFF_DO + NS * Q_TILE;      // one dS^T tile (hi + lo in split mode)
+    static constexpr int OFF_VEC = OFF_DS + DS_TILE;         // NS x (lse[64], delta[64]) floats
     static constexpr int OFF_BAR = OFF_VEC + NS * 2 * BQ * 4;
     static constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
     static constexpr int THREADS = 512;
@@ -79,11 +87,12 @@ struct BwdParams {
     float scale, scale_log2;
 };
 
-// TMEM column of the packed bf16 pair that starts k-step ks (16 queries) of P^T / dS^T:
-// queries 0-31 live in columns 0-15, queries 32-63 in columns 32-47 (each compute
-// warpgroup overwrites only the columns it has itself read).
-// In split mode the hi part takes the first 16 of a warpgroup's 32 columns and the lo part the next 16.
-__device__ __forceinline__ uint32_t bwd_pcol(int ks, int lo_part = 0) { return static_cast<uint32_t>((ks >> 1) * 32 + (ks & 1) * 8 + lo_part * 16); }
+// TMEM column of the packed bf16 pair that starts k-step ks (16 queries) of a P^T / dS^T operand.
+// Each compute warpgroup owns 32 columns of a 64-column buffer (queries 0-31 -> columns 0-31,
+// queries 32-63 -> columns 32-63) and writes only there; inside its 32 columns the first 16 hold
+// "part 0" and the next 16 "part 1".  bf16 mode: S^T buffer = {P^T, dS^T}.  Split mode: S^T
+// buffer = {P^T hi, P^T lo}, dP^T buffer = {dS^T hi, dS^T lo}.
+__device__ __forceinline__ uint32_t bwd_pcol(int ks, int part = 0) { return static_cast<uint32_t>((ks >> 1) * 32 + (ks & 1) * 8 + part * 16); }
 
 // acc[128 keys x 64 queries] = A B^T with A = K or V tile, B = Q or dO block, both K-major (S^T and dP^T).
 template <class TR>
@@ -105,11 +114,11 @@ __device__ __forceinline__ void bwd_issue_kmajor(uint32_t tmem_acc, uint32_t a_s
 
 // acc[128 keys x D] += A B with A = P^T or dS^T in TMEM (64 queries), B = dO or Q block, MN-major (dV and dK).
 template <class TR>
-__device__ __forceinline__ void bwd_issue_acc(uint32_t tmem_acc, uint32_t tmem_a, uint32_t b_saddr, bool accumulate) {
+__device__ __forceinline__ void bwd_issue_acc(uint32_t tmem_acc, uint32_t tmem_a, int part, uint32_t b_saddr, bool accumulate) {
     if constexpr (!TR::SPLIT) {
 #pragma unroll
         for (int ks = 0; ks < TR::BQ / 16; ++ks)
-            umma_ts_f16(tmem_acc, tmem_a + bwd_pcol(ks), make_sdesc_sw128(b_saddr + ks * 2048, TR::Q_PANEL, 1024), TR::IDESC_DKV,
+            umma_ts_f16(tmem_acc, tmem_a + bwd_pcol(ks, part), make_sdesc_sw128(b_saddr + ks * 2048, TR::Q_PANEL, 1024), TR::IDESC_DKV,
                         (accumulate || ks > 0) ? 1u : 0u);
     } else {
 #pragma unroll
@@ -158,14 +167,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     float* sVec = reinterpret_cast<float*>(smem + TR::OFF_VEC);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TR::OFF_BAR);
     uint64_t* kv_full = bars;               // [1]
-    uint64_t* qdo_full = bars + 1;          // [NS]
-    uint64_t* qdo_empty = qdo_full + NS;    // [NS]
-    uint64_t* st_full = qdo_empty + NS;     // [2]
-    uint64_t* dp_full = st_full + 2;        // [2]
-    uint64_t* p_full = dp_full + 2;         // [2]
-    uint64_t* ds_full = p_full + 2;         // [2]
-    uint64_t* dq_full = ds_full + 2;        // [2]
-    uint64_t* dq_empty = dq_full + 2;       // [2]
+    uint64_t* qdo_full = bars + 1;          // [NS]  TMA: Q, dO tiles + staged lse/delta
+    uint64_t* qdo_empty = qdo_full + NS;    // [NS]  MMA commit: block consumed
+    uint64_t* sdp_full = qdo_empty + NS;    // [2]   MMA commit: S^T and dP^T of a block are in TMEM
+    uint64_t* pds_full = sdp_full + 2;      // [2]   compute warps: P^T, dS^T written (TMEM + smem)
+    uint64_t* dq_full = pds_full + 2;       // [2]   MMA commit: dQ^T in TMEM (and the dS^T smem tile is free)
+    uint64_t* dq_empty = dq_full + 2;       // [2]   drain warps: dQ^T copied to registers
     uint64_t* dkv_full = dq_empty + 2;      // [1]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dkv_full + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -184,7 +191,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_init(kv_full, 1);
         for (int s = 0; s < NS; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(&st_full[b], 1); mbar_init(&dp_full[b], 1); mbar_init(&p_full[b], 8); mbar_init(&ds_full[b], 8);
+            mbar_init(&sdp_full[b], 1); mbar_init(&pds_full[b], 8);
             mbar_init(&dq_full[b], 1); mbar_init(&dq_empty[b], 4);
         }
         mbar_init(dkv_full, 1);
@@ -200,6 +207,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
+    if (warp >= 12) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+    } else if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 112;");
+    }
+
     if (warp == 12) {
         // ------------------------------ producer ------------------------------
         if (lane == 0) {
@@ -214,15 +227,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const int s = it % NS;
             const int m = m0 + it;
             mbar_wait(&qdo_empty[s], ((it / NS) & 1) ^ 1, ab, 10);
-            // per-row vectors: lse pre-multiplied by log2(e); rows past T get +inf so that P = 0
+            // per-row vectors, both negated so the compute warps can use packed add / fma directly:
+            // -lse * log2(e) (rows past T get -inf so that P = 0) and -delta
             float* v_lse = sVec + s * 2 * BQ;
             float* v_del = v_lse + BQ;
 #pragma unroll
             for (int e = lane; e < BQ; e += 32) {
                 const int qg = m * BQ + e;
                 const bool ok = qg < T;
-                v_lse[e] = ok ? prm.lse[static_cast<size_t>(bh) * T + qg] * 1.4426950408889634f : INFINITY;
-                v_del[e] = ok ? prm.delta[static_cast<size_t>(bh) * T + qg] : 0.f;
+                v_lse[e] = ok ? prm.lse[static_cast<size_t>(bh) * T + qg] * -1.4426950408889634f : -INFINITY;
+                v_del[e] = ok ? -prm.delta[static_cast<size_t>(bh) * T + qg] : 0.f;
             }
             __syncwarp();
             if (lane == 0) {
@@ -237,118 +251,121 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     } else if (warp == 13) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+            const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDS = smem_u32(sDS);
             mbar_wait(kv_full, 0, ab, 20);
-            for (int it = 0; it <= nblk; ++it) {
+            // S^T(blk) and dP^T(blk) into buffer blk & 1; the dP^T buffer must have been drained of dQ^T(blk - 2)
+            auto issue_front = [&](int blk) {
+                const int b = blk & 1, s = blk % NS;
+                mbar_wait(&qdo_full[s], (blk / NS) & 1, ab, 21);
+                tc_fence_after_sync();
+                bwd_issue_kmajor<TR>(tmem + TR::TM_ST + b * 64, aK, smem_u32(sQ + s * TR::Q_TILE));
+                if (blk >= 2) { mbar_wait(&dq_empty[b], ((blk - 2) >> 1) & 1, ab, 24); tc_fence_after_sync(); }
+                bwd_issue_kmajor<TR>(tmem + TR::TM_DP + b * 64, aV, smem_u32(sDO + s * TR::Q_TILE));
+                umma_commit(&sdp_full[b]);
+            };
+            issue_front(0);
+            if (nblk > 1) issue_front(1);
+            for (int it = 0; it < nblk; ++it) {
                 const int b = it & 1, s = it % NS;
                 const uint32_t aQ = smem_u32(sQ + s * TR::Q_TILE), aDO = smem_u32(sDO + s * TR::Q_TILE);
-                if (it < nblk) {
-                    mbar_wait(&qdo_full[s], (it / NS) & 1, ab, 21);
-                    tc_fence_after_sync();
-                    // S^T(it) = K Q^T
-                    bwd_issue_kmajor<TR>(tmem + TR::TM_ST + b * 64, aK, aQ);
-                    umma_commit(&st_full[b]);
+                const uint32_t t_st = tmem + TR::TM_ST + b * 64, t_dp = tmem + TR::TM_DP + b * 64;
+                mbar_wait(&pds_full[b], (it >> 1) & 1, ab, 22);
+                tc_fence_after_sync();
+                if constexpr (!TR::SPLIT) {
+                    bwd_issue_dq<TR>(t_dp, aK, aDS);                            // dQ^T(it) over the consumed dP^T buffer
+                    umma_commit(&dq_full[b]);
+                    bwd_issue_acc<TR>(tmem + TR::TM_DK, t_st, 1, aQ, it > 0);   // dK += dS^T Q
+                    bwd_issue_acc<TR>(tmem + TR::TM_DV, t_st, 0, aDO, it > 0);  // dV += P^T dO
+                } else {
+                    bwd_issue_acc<TR>(tmem + TR::TM_DV, t_st, 0, aDO, it > 0);
+                    bwd_issue_acc<TR>(tmem + TR::TM_DK, t_dp, 0, aQ, it > 0);
+                    bwd_issue_dq<TR>(t_dp, aK, aDS);
+                    umma_commit(&dq_full[b]);
                 }
-                const int j = it - 1, bj = j & 1, sj = j % NS;
-                const uint32_t aQj = smem_u32(sQ + sj * TR::Q_TILE), aDOj = smem_u32(sDO + sj * TR::Q_TILE);
-                if (j >= 0) {
-                    // dV += P^T(j) dO(j)
-                    mbar_wait(&p_full[bj], (j >> 1) & 1, ab, 22);
-                    tc_fence_after_sync();
-                    bwd_issue_acc<TR>(tmem + TR::TM_DV, tmem + TR::TM_ST + bj * 64, aDOj, j > 0);
-                    // dK += dS^T(j) Q(j)
-                    mbar_wait(&ds_full[bj], (j >> 1) & 1, ab, 23);
-                    tc_fence_after_sync();
-                    bwd_issue_acc<TR>(tmem + TR::TM_DK, tmem + TR::TM_DP + bj * 64, aQj, j > 0);
-                }
-                if (it < nblk) {
-                    // dP^T(it) = V dO^T, into the buffer the drain of dQ^T(it-2) has released
-                    if (it >= 2) { mbar_wait(&dq_empty[b], ((it - 2) >> 1) & 1, ab, 24); tc_fence_after_sync(); }
-                    bwd_issue_kmajor<TR>(tmem + TR::TM_DP + b * 64, aV, aDO);
-                    umma_commit(&dp_full[b]);
-                }
-                if (j >= 0) {
-                    // dQ^T(j) = K^T dS^T(j), over the dS^T/dP^T buffer that dK(j) has just consumed
-                    const uint32_t aDS = smem_u32(sDS + bj * TR::DS_TILE);
-                    bwd_issue_dq<TR>(tmem + TR::TM_DP + bj * 64, aK, aDS);
-                    umma_commit(&dq_full[bj]);
-                    umma_commit(&qdo_empty[sj]);
-                }
+                umma_commit(&qdo_empty[s]);
+                if (it + 2 < nblk) issue_front(it + 2);
             }
             umma_commit(dkv_full);
         }
     } else if (warp < 8) {
         // ------------------------------ compute: P^T and dS^T ------------------------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 160;");
         const int h = warp >> 2;                     // which 32 query columns
         const int wq = warp & 3;
         const int r = wq * 32 + lane;                // key row inside the tile
         const int kv_g = n * BKV + r;
         const bool row_dead = kv_g >= T;
+        const bool tail_tile = (n + 1) * BKV > T;     // this key tile has rows past T
         const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
         const float c = prm.scale_log2;
 
         for (int it = 0; it < nblk; ++it) {
             const int b = it & 1, s = it % NS, m = m0 + it;
-            const uint32_t par = (it >> 1) & 1;
             const float* v_lse = sVec + s * 2 * BQ + h * 32;
             const float* v_del = v_lse + BQ;
             const uint32_t t_st = tmem + TR::TM_ST + b * 64 + h * 32 + lane_base;
             const uint32_t t_dp = tmem + TR::TM_DP + b * 64 + h * 32 + lane_base;
             mbar_wait(&qdo_full[s], (it / NS) & 1, ab, 30);      // lse / delta visible
-            mbar_wait(&st_full[b], par, ab, 31);
+            mbar_wait(&sdp_full[b], (it >> 1) & 1, ab, 31);
             tc_fence_after_sync();
-            uint32_t sr[32];
+            uint32_t sr[32], dr[32];
             tmem_ld_x32(t_st, sr);
+            tmem_ld_x32(t_dp, dr);
             tmem_wait_ld();
-            float p[32];
             const bool diag = prm.causal && (m * BQ < (n + 1) * BKV);
             const int q0 = m * BQ + h * 32;
+            const bool masked = diag || tail_tile;             // uniform per block: most blocks take the unmasked path
+            uint32_t pk[16], dk[16], pl[16], dl[16];
+            const uint64_t c2 = pack_f32x2(c, c);
+            const float4* v_lse4 = reinterpret_cast<const float4*>(v_lse);
+            const float4* v_del4 = reinterpret_cast<const float4*>(v_del);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-                float x = fast_exp2(fmaf(__uint_as_float(sr[e]), c, -v_lse[e]));
-                if (row_dead || (diag && kv_g > q0 + e)) x = 0.f;
-                p[e] = x;
-            }
-            uint32_t pk[16], pl[16];
+            for (int e4 = 0; e4 < 8; ++e4) {
+                const float4 nl = v_lse4[e4], nd = v_del4[e4];   // broadcast 16-byte loads: 4 query columns each
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-                pk[e] = pack_bf16x2(p[2 * e], p[2 * e + 1]);
-                if constexpr (TR::SPLIT)
-                    pl[e] = pack_bf16x2(p[2 * e] - __uint_as_float(pk[e] << 16), p[2 * e + 1] - __uint_as_float(pk[e] & 0xffff0000u));
+                for (int half = 0; half < 2; ++half) {
+                    const int e = e4 * 4 + half * 2;
+                    const uint64_t nl2 = half ? pack_f32x2(nl.z, nl.w) : pack_f32x2(nl.x, nl.y);
+                    const uint64_t nd2 = half ? pack_f32x2(nd.z, nd.w) : pack_f32x2(nd.x, nd.y);
+                    float x0, x1;
+                    unpack_f32x2(ffma2(pack_f32x2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])), c2, nl2), x0, x1);
+                    float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                    if (masked) {
+                        if (row_dead || (diag && kv_g > q0 + e)) p0 = 0.f;
+                        if (row_dead || (diag && kv_g > q0 + e + 1)) p1 = 0.f;
+                    }
+                    const uint64_t p2 = pack_f32x2(p0, p1);
+                    float d0, d1;
+                    unpack_f32x2(fmul2(p2, fadd2(pack_f32x2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])), nd2)), d0, d1);
+                    pk[e >> 1] = pack_bf16x2(p0, p1);
+                    dk[e >> 1] = pack_bf16x2(d0, d1);
+                    if constexpr (TR::SPLIT) {
+                        pl[e >> 1] = pack_bf16x2(p0 - __uint_as_float(pk[e >> 1] << 16), p1 - __uint_as_float(pk[e >> 1] & 0xffff0000u));
+                        dl[e >> 1] = pack_bf16x2(d0 - __uint_as_float(dk[e >> 1] << 16), d1 - __uint_as_float(dk[e >> 1] & 0xffff0000u));
+                    }
+                }
             }
             tmem_st_x16(t_st, pk);
-            if constexpr (TR::SPLIT) tmem_st_x16(t_st + 16, pl);
-            tmem_wait_st();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[b]);
-
-            mbar_wait(&dp_full[b], par, ab, 32);
-            tc_fence_after_sync();
-            tmem_ld_x32(t_dp, sr);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-                const float d0 = p[2 * e] * (__uint_as_float(sr[2 * e]) - v_del[2 * e]);
-                const float d1 = p[2 * e + 1] * (__uint_as_float(sr[2 * e + 1]) - v_del[2 * e + 1]);
-                pk[e] = pack_bf16x2(d0, d1);
-                if constexpr (TR::SPLIT)
-                    pl[e] = pack_bf16x2(d0 - __uint_as_float(pk[e] << 16), d1 - __uint_as_float(pk[e] & 0xffff0000u));
+            if constexpr (!TR::SPLIT) {
+                tmem_st_x16(t_st + 16, dk);
+            } else {
+                tmem_st_x16(t_st + 16, pl);
+                tmem_st_x16(t_dp, dk);
+                tmem_st_x16(t_dp + 16, dl);
             }
-            tmem_st_x16(t_dp, pk);
-            if constexpr (TR::SPLIT) tmem_st_x16(t_dp + 16, pl);
-            uint8_t* ds_row = sDS + b * TR::DS_TILE;
+            // the single dS^T smem tile is free once dQ^T of the previous block has completed
+            if (it >= 1) mbar_wait(&dq_full[(it - 1) & 1], ((it - 1) >> 1) & 1, ab, 32);
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) {
-                *reinterpret_cast<uint4*>(ds_row + sw128_offset(r, h * 4 + c4)) = make_uint4(pk[4 * c4], pk[4 * c4 + 1], pk[4 * c4 + 2], pk[4 * c4 + 3]);
+                *reinterpret_cast<uint4*>(sDS + sw128_offset(r, h * 4 + c4)) = make_uint4(dk[4 * c4], dk[4 * c4 + 1], dk[4 * c4 + 2], dk[4 * c4 + 3]);
                 if constexpr (TR::SPLIT)
-                    *reinterpret_cast<uint4*>(ds_row + TR::DS_PART + sw128_offset(r, h * 4 + c4)) = make_uint4(pl[4 * c4], pl[4 * c4 + 1], pl[4 * c4 + 2], pl[4 * c4 + 3]);
+                    *reinterpret_cast<uint4*>(sDS + TR::DS_PART + sw128_offset(r, h * 4 + c4)) = make_uint4(dl[4 * c4], dl[4 * c4 + 1], dl[4 * c4 + 2], dl[4 * c4 + 3]);
             }
             tmem_wait_st();
             fence_proxy_async_smem();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&ds_full[b]);
+            if (lane == 0) mbar_arrive(&pds_full[b]);
         }
 
         // ---- epilogue: warps 0-3 write dV, warps 4-7 write dK (scaled) ----
@@ -417,12 +434,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (lane_ok) {
                 float* base = prm.dq_acc + (static_cast<size_t>(bh) * T + static_cast<size_t>(m) * BQ) * D + d;
                 const int rows = min(BQ, T - m * BQ);
+                if (rows == BQ) {
 #pragma unroll
-                for (int e = 0; e < 32; ++e)
-                    if (e < rows) atomicAdd(base + static_cast<size_t>(e) * D, __uint_as_float(r0[e]));
+                    for (int e = 0; e < 32; ++e) atomicAdd(base + e * D, __uint_as_float(r0[e]));
 #pragma unroll
-                for (int e = 0; e < 32; ++e)
-                    if (32 + e < rows) atomicAdd(base + static_cast<size_t>(32 + e) * D, __uint_as_float(r1[e]));
+                    for (int e = 0; e < 32; ++e) atomicAdd(base + (32 + e) * D, __uint_as_float(r1[e]));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        if (e < rows) atomicAdd(base + e * D, __uint_as_float(r0[e]));
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        if (32 + e < rows) atomicAdd(base + (32 + e) * D, __uint_as_float(r1[e]));
+                }
             }
         }
     }
