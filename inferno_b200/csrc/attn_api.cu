@@ -76,8 +76,9 @@ int check_common(int B, int H, int T, int D, int dtype, int math_mode, int causa
 }
 
 size_t fwd_ws_bytes(long N, bool f32) { return kHeaderBytes + (f32 ? 6 * round_up(N * 2, 256) : 0); }
+inline int pad64(int T) { return (T + 63) / 64 * 64; }
 size_t bwd_ws_bytes(long N, long BH, int T, bool f32) {
-    return kHeaderBytes + round_up(N * 4, 256) /*dq accumulator*/ + round_up(static_cast<size_t>(BH) * T * 4, 256) /*delta*/ +
+    return kHeaderBytes + round_up(N * 4, 256) /*dq accumulator*/ + 2 * round_up(static_cast<size_t>(BH) * pad64(T) * 4, 256) /*-delta, -lse*log2e*/ +
            (f32 ? 8 * round_up(N * 2, 256) : 0);
 }
 
@@ -123,7 +124,7 @@ int launch_fwd(const void* q, const void* q_lo, const void* k, const void* k_lo,
 
 template <class TR>
 int launch_bwd(const void* const q[2], const void* const k[2], const void* const v[2], const void* const dO[2],
-               const float* lse, const float* delta, float* dq_acc, void* dk, void* dv, int* status, long BH, int T,
+               const float* nlse2, const float* ndelta, int T_pad, float* dq_acc, void* dk, void* dv, int* status, long BH, int T,
                float scale, int causal, cudaStream_t stream) {
     CUtensorMap tq[2], tk[2], tv[2], tdo[2], tdk, tdv;
     for (int i = 0; i < (TR::SPLIT ? 2 : 1); ++i) {
@@ -137,8 +138,9 @@ int launch_bwd(const void* const q[2], const void* const k[2], const void* const
     if (!cuda_ok(cudaFuncSetAttribute(attn_bwd_kernel<TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::SMEM_BYTES)))
         return IB200_ERR_CUDA;
     BwdParams prm;
-    prm.lse = lse;
-    prm.delta = delta;
+    prm.nlse2 = nlse2;
+    prm.ndelta = ndelta;
+    prm.T_pad = T_pad;
     prm.dq_acc = dq_acc;
     prm.status = status;
     prm.T = T;
@@ -163,11 +165,14 @@ int launch_bwd_all(const void* q, const void* k, const void* v, const void* o, c
     int* status = reinterpret_cast<int*>(ws);
     float* dq_acc = reinterpret_cast<float*>(ws + kHeaderBytes);
     uint8_t* after_acc = ws + kHeaderBytes + round_up(N * 4, 256);
-    float* delta = reinterpret_cast<float*>(after_acc);
+    const int T_pad = pad64(T);
+    const size_t vec_bytes = round_up(static_cast<size_t>(BH) * T_pad * 4, 256);
+    float* ndelta = reinterpret_cast<float*>(after_acc);
+    float* nlse2 = reinterpret_cast<float*>(after_acc + vec_bytes);
     if (!cuda_ok(cudaMemsetAsync(ws, 0, kHeaderBytes + round_up(N * 4, 256), stream))) return IB200_ERR_CUDA;
     int rc;
     if (f32) {
-        uint8_t* base = after_acc + round_up(static_cast<size_t>(BH) * T * 4, 256);
+        uint8_t* base = after_acc + 2 * vec_bytes;
         const size_t slab = round_up(N * 2, 256);
         const void* part[8];
         const float* src[4] = {static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v), static_cast<const float*>(dO)};
@@ -177,18 +182,18 @@ int launch_bwd_all(const void* q, const void* k, const void* v, const void* o, c
             rc = launch_split_bf16(src[i], const_cast<void*>(part[2 * i]), const_cast<void*>(part[2 * i + 1]), N, stream);
             if (rc) return rc;
         }
-        rc = launch_delta<64, true>(o, dO, delta, BH * T, stream); if (rc) return rc;
-        rc = launch_bwd<BwdTraits<64, true>>(&part[0], &part[2], &part[4], &part[6], lse, delta, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
+        rc = launch_delta<64, true>(o, dO, lse, ndelta, nlse2, BH, T, T_pad, stream); if (rc) return rc;
+        rc = launch_bwd<BwdTraits<64, true>>(&part[0], &part[2], &part[4], &part[6], nlse2, ndelta, T_pad, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
         if (rc) return rc;
         return launch_dq_finish<true>(dq_acc, dq, scale, N, stream);
     }
     const void* qq[2] = {q, q}; const void* kk[2] = {k, k}; const void* vv[2] = {v, v}; const void* dd[2] = {dO, dO};
     if (D == 64) {
-        rc = launch_delta<64, false>(o, dO, delta, BH * T, stream); if (rc) return rc;
-        rc = launch_bwd<BwdTraits<64, false>>(qq, kk, vv, dd, lse, delta, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
+        rc = launch_delta<64, false>(o, dO, lse, ndelta, nlse2, BH, T, T_pad, stream); if (rc) return rc;
+        rc = launch_bwd<BwdTraits<64, false>>(qq, kk, vv, dd, nlse2, ndelta, T_pad, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
     } else {
-        rc = launch_delta<128, false>(o, dO, delta, BH * T, stream); if (rc) return rc;
-        rc = launch_bwd<BwdTraits<128, false>>(qq, kk, vv, dd, lse, delta, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
+        rc = launch_delta<128, false>(o, dO, lse, ndelta, nlse2, BH, T, T_pad, stream); if (rc) return rc;
+        rc = launch_bwd<BwdTraits<128, false>>(qq, kk, vv, dd, nlse2, ndelta, T_pad, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
     }
     if (rc) return rc;
     return launch_dq_finish<false>(dq_acc, dq, scale, N, stream);

@@ -1,7 +1,7 @@
 // Bandwidth-bound helper kernels around the attention main kernels:
 //   * split_bf16   fp32 x -> (hi, lo) bf16 pair with hi = bf16(x), lo = bf16(x - hi); the
 //                  fp32-I/O kernels multiply such pairs in three bf16 MMAs
-//   * delta        delta[row] = sum_d O[row,d] * dO[row,d]; this is the reference's
+//   * delta        -delta[row] = -sum_d O[row,d] * dO[row,d] (and -lse*log2e beside it); this is the reference's
 //                  dot = sum_j dP_ij P_ij (src/inferno/gradfn/softmaxbackward.h:101-109)
 //                  rewritten so that it needs no [T,T] matrix
 //   * dq_finish    dQ = scale * accumulator, cast to the output type; the scale is
@@ -46,44 +46,61 @@ inline int launch_split_bf16(const float* in, void* hi, void* lo, long n, cudaSt
 }
 
 // One row of D elements is covered by TPR threads, each loading 16 bytes of O and of dO.
+// Outputs are laid out [heads, T_pad] with T_pad a multiple of 64 so that the backward kernel can
+// fetch the 64 values of a query block with one aligned bulk copy; both are stored negated and
+// pre-scaled the way that kernel consumes them:
+//   ndelta[h, t] = -sum_d O[h,t,d] * dO[h,t,d]        nlse2[h, t] = -lse[h,t] * log2(e)
+// Padding rows (t >= T) are written as 0.
 template <int D, bool F32>
-__global__ void __launch_bounds__(kAuxThreads) delta_kernel(const void* __restrict__ o_, const void* __restrict__ do_, float* __restrict__ delta, long rows) {
+__global__ void __launch_bounds__(kAuxThreads) delta_kernel(const void* __restrict__ o_, const void* __restrict__ do_, const float* __restrict__ lse,
+                                                            float* __restrict__ ndelta, float* __restrict__ nlse2, long heads, int T, int T_pad) {
     constexpr int EPT = F32 ? 4 : 8;              // elements per 16-byte load
     constexpr int TPR = D / EPT;                  // threads per row (8 or 16)
     constexpr int RPB = kAuxThreads / TPR;        // rows per block per step
     const int sub = threadIdx.x % TPR;
+    const long rows_pad = heads * T_pad;
     const long row0 = blockIdx.x * static_cast<long>(RPB) + threadIdx.x / TPR;
-    for (long row = row0; row < rows; row += static_cast<long>(gridDim.x) * RPB) {
+    for (long prow = row0; prow < rows_pad; prow += static_cast<long>(gridDim.x) * RPB) {
+        const long head = prow / T_pad;
+        const int t = static_cast<int>(prow - head * T_pad);
+        const bool live = t < T;
+        const long row = head * T + t;
         float acc = 0.f;
-        if constexpr (F32) {
-            const float4 a = reinterpret_cast<const float4*>(o_)[row * TPR + sub];
-            const float4 b = reinterpret_cast<const float4*>(do_)[row * TPR + sub];
-            acc = a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
-        } else {
-            const uint4 a = reinterpret_cast<const uint4*>(o_)[row * TPR + sub];
-            const uint4 b = reinterpret_cast<const uint4*>(do_)[row * TPR + sub];
-            const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-            const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+        if (live) {
+            if constexpr (F32) {
+                const float4 a = reinterpret_cast<const float4*>(o_)[row * TPR + sub];
+                const float4 b = reinterpret_cast<const float4*>(do_)[row * TPR + sub];
+                acc = a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+            } else {
+                const uint4 a = reinterpret_cast<const uint4*>(o_)[row * TPR + sub];
+                const uint4 b = reinterpret_cast<const uint4*>(do_)[row * TPR + sub];
+                const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+                const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 fa = __bfloat1622float2(pa[e]), fb = __bfloat1622float2(pb[e]);
-                acc = fmaf(fa.x, fb.x, acc);
-                acc = fmaf(fa.y, fb.y, acc);
+                for (int e = 0; e < 4; ++e) {
+                    const float2 fa = __bfloat1622float2(pa[e]), fb = __bfloat1622float2(pb[e]);
+                    acc = fmaf(fa.x, fb.x, acc);
+                    acc = fmaf(fa.y, fb.y, acc);
+                }
             }
         }
 #pragma unroll
         for (int off = TPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-        if (sub == 0) delta[row] = acc;
+        if (sub == 0) {
+            ndelta[prow] = -acc;
+            nlse2[prow] = live ? lse[row] * -1.4426950408889634f : 0.f;
+        }
     }
 }
 
 template <int D, bool F32>
-inline int launch_delta(const void* o, const void* dO, float* delta, long rows, cudaStream_t stream) {
+inline int launch_delta(const void* o, const void* dO, const float* lse, float* ndelta, float* nlse2, long heads, int T, int T_pad,
+                        cudaStream_t stream) {
     constexpr int RPB = kAuxThreads / (D / (F32 ? 4 : 8));
     // every thread of a block takes part in the shuffles: the row loop bound is uniform per TPR group
-    long blocks = (rows + RPB - 1) / RPB;
+    long blocks = (heads * T_pad + RPB - 1) / RPB;
     if (blocks > kAuxBlocks) blocks = kAuxBlocks;
-    delta_kernel<D, F32><<<static_cast<int>(blocks), kAuxThreads, 0, stream>>>(o, dO, delta, rows);
+    delta_kernel<D, F32><<<static_cast<int>(blocks), kAuxThreads, 0, stream>>>(o, dO, lse, ndelta, nlse2, heads, T, T_pad);
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 

@@ -79,8 +79,9 @@ struct BwdTraits {
 };
 
 struct BwdParams {
-    const float* lse;      // [BH, T]
-    const float* delta;    // [BH, T]
+    const float* nlse2;    // [BH, T_pad]  -lse * log2(e), 0 in the padding
+    const float* ndelta;   // [BH, T_pad]  -rowsum(dO * O), 0 in the padding
+    int T_pad;             // T rounded up to a multiple of 64
     float* dq_acc;         // [BH, T, D] fp32, zeroed before launch
     int* status;
     int T, BH, causal;
@@ -223,29 +224,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 tma_load_3d(sV + p * TR::KV_PANEL, lo ? &tm_v_lo : &tm_v, kv_full, TR::SPLIT ? 0 : p * 64, n * BKV, bh);
             }
         }
-        for (int it = 0; it < nblk; ++it) {
-            const int s = it % NS;
-            const int m = m0 + it;
-            mbar_wait(&qdo_empty[s], ((it / NS) & 1) ^ 1, ab, 10);
-            // per-row vectors, both negated so the compute warps can use packed add / fma directly:
-            // -lse * log2(e) (rows past T get -inf so that P = 0) and -delta
-            float* v_lse = sVec + s * 2 * BQ;
-            float* v_del = v_lse + BQ;
-#pragma unroll
-            for (int e = lane; e < BQ; e += 32) {
-                const int qg = m * BQ + e;
-                const bool ok = qg < T;
-                v_lse[e] = ok ? prm.lse[static_cast<size_t>(bh) * T + qg] * -1.4426950408889634f : -INFINITY;
-                v_del[e] = ok ? -prm.delta[static_cast<size_t>(bh) * T + qg] : 0.f;
-            }
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive_expect_tx(&qdo_full[s], 2 * TR::Q_TILE);
+        if (lane == 0) {
+            for (int it = 0; it < nblk; ++it) {
+                const int s = it % NS;
+                const int m = m0 + it;
+                mbar_wait(&qdo_empty[s], ((it / NS) & 1) ^ 1, ab, 10);
+                mbar_arrive_expect_tx(&qdo_full[s], 2 * TR::Q_TILE + 2 * BQ * 4);
                 for (int p = 0; p < TR::NP; ++p) {
                     const bool lo = TR::SPLIT && p;
                     tma_load_3d(sQ + s * TR::Q_TILE + p * TR::Q_PANEL, lo ? &tm_q_lo : &tm_q, &qdo_full[s], TR::SPLIT ? 0 : p * 64, m * BQ, bh);
                     tma_load_3d(sDO + s * TR::Q_TILE + p * TR::Q_PANEL, lo ? &tm_do_lo : &tm_do, &qdo_full[s], TR::SPLIT ? 0 : p * 64, m * BQ, bh);
                 }
+                // the block's 64 values of -lse*log2e and of -delta (padded rows, so always aligned and in range)
+                const size_t voff = static_cast<size_t>(bh) * prm.T_pad + static_cast<size_t>(m) * BQ;
+                bulk_load_1d(sVec + s * 2 * BQ, prm.nlse2 + voff, BQ * 4, &qdo_full[s]);
+                bulk_load_1d(sVec + s * 2 * BQ + BQ, prm.ndelta + voff, BQ * 4, &qdo_full[s]);
             }
         }
     } else if (warp == 13) {
