@@ -135,13 +135,25 @@ int launch_bwd(const void* const q[2], const void* const k[2], const void* const
     if (!TR::SPLIT) { tq[1] = tq[0]; tk[1] = tk[0]; tv[1] = tv[0]; tdo[1] = tdo[0]; }
     if (!make_tmap(&tdk, dk, TR::SPLIT, TR::D, T, BH, TR::BKV) || !make_tmap(&tdv, dv, TR::SPLIT, TR::D, T, BH, TR::BKV))
         return IB200_ERR_CUDA;
+    // fp32 dQ accumulator, whole rows of D floats per box row, no swizzle (the staging tile is plain row-major)
+    CUtensorMap tdq;
+    {
+        EncodeTiledFn enc = encode_fn();
+        if (!enc) return IB200_ERR_CUDA;
+        cuuint64_t dims[3] = {static_cast<cuuint64_t>(TR::D), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(BH)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(TR::D) * 4, static_cast<cuuint64_t>(T) * TR::D * 4};
+        cuuint32_t box[3] = {static_cast<cuuint32_t>(TR::D), static_cast<cuuint32_t>(TR::BQ), 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        if (enc(&tdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, dq_acc, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return IB200_ERR_CUDA;
+    }
     if (!cuda_ok(cudaFuncSetAttribute(attn_bwd_kernel<TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::SMEM_BYTES)))
         return IB200_ERR_CUDA;
     BwdParams prm;
     prm.nlse2 = nlse2;
     prm.ndelta = ndelta;
     prm.T_pad = T_pad;
-    prm.dq_acc = dq_acc;
     prm.status = status;
     prm.T = T;
     prm.BH = static_cast<int>(BH);
@@ -151,7 +163,7 @@ int launch_bwd(const void* const q[2], const void* const k[2], const void* const
     if (BH > 65535) return IB200_ERR_UNSUPPORTED;
     dim3 grid((T + TR::BKV - 1) / TR::BKV, static_cast<unsigned>(BH), 1);
     if (g_ev[2]) cudaEventRecord(g_ev[2], stream);
-    attn_bwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq[0], tq[1], tk[0], tk[1], tv[0], tv[1], tdo[0], tdo[1], tdk, tdv, prm);
+    attn_bwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq[0], tq[1], tk[0], tk[1], tv[0], tv[1], tdo[0], tdo[1], tdk, tdv, tdq, prm);
     if (g_ev[3]) cudaEventRecord(g_ev[3], stream);
     return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
 }

@@ -18,8 +18,10 @@
 //   dV  += P^T dO       TMEM x smem (dO MN-major)   -> TMEM DV
 //   dK  += dS^T Q       TMEM x smem (Q MN-major)    -> TMEM DK
 //   dQ^T = K^T dS^T     smem (K MN-major) x smem (dS^T MN-major) -> TMEM DP[b]  (M=D, N=64)
-// dQ^T leaves through coalesced fp32 reductions into a scratch accumulator
-// (lane = head-dim index, so a warp adds 32 consecutive floats per instruction).
+// dQ^T is transposed through shared memory (lane = head-dim index, so a warp writes 32
+// consecutive floats per store, conflict-free) and added to the fp32 scratch accumulator
+// by a TMA reduction (cp.reduce.async.bulk.tensor .add), which keeps the adds off the
+// load/store pipe the compute warps depend on.
 //
 // Software pipeline of the MMA issuer (block = one 64-row query block, b = block & 1):
 //   prologue   S^T(0) dP^T(0) S^T(1) dP^T(1)
@@ -56,7 +58,7 @@ struct BwdTraits {
     static constexpr int Q_PANEL = BQ * 128, Q_TILE = NP * Q_PANEL;
     static constexpr int DS_PART = BKV * 128;                // [128 keys x 64 queries] bf16
     static constexpr int DS_TILE = (SPLIT ? 2 : 1) * DS_PART;
-    static constexpr int NS = SPLIT ? 3 : 4;                 // Q/dO ring depth
+    static constexpr int NS = 3;                             // Q/dO ring depth
     static constexpr int NTERMS = SPLIT ? 3 : 1;
     static constexpr int OUT_TILE = SPLIT ? BKV * D * 4 : KV_TILE;   // dK / dV staging bytes
     static constexpr int OUT_PANELS = SPLIT ? 2 : D / 64;
@@ -70,7 +72,9 @@ struct BwdTraits {
     static constexpr int OFF_Q = OFF_V + KV_TILE;            // NS tiles; ring start, reused as dV/dK staging
     static constexpr int OFF_DO = OFF_Q + NS * Q_TILE;       // NS tiles
     static constexpr int OFF_DS = OFF_DO + NS * Q_TILE;      // one dS^T tile (hi + lo in split mode)
-    static constexpr int OFF_VEC = OFF_DS + DS_TILE;         // NS x (lse[64], delta[64]) floats
+    static constexpr int OFF_DQ = OFF_DS + DS_TILE;          // dQ staging [64 queries x D] fp32, row-major, for the TMA reduction
+    static constexpr int DQ_STAGE = BQ * D * 4;
+    static constexpr int OFF_VEC = OFF_DQ + DQ_STAGE;     // NS x (lse[64], delta[64]) floats
     static constexpr int OFF_BAR = OFF_VEC + NS * 2 * BQ * 4;
     static constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
     static constexpr int THREADS = 512;
@@ -82,7 +86,6 @@ struct BwdParams {
     const float* nlse2;    // [BH, T_pad]  -lse * log2(e), 0 in the padding
     const float* ndelta;   // [BH, T_pad]  -rowsum(dO * O), 0 in the padding
     int T_pad;             // T rounded up to a multiple of 64
-    float* dq_acc;         // [BH, T, D] fp32, zeroed before launch
     int* status;
     int T, BH, causal;
     float scale, scale_log2;
@@ -95,31 +98,34 @@ struct BwdParams {
 // buffer = {P^T hi, P^T lo}, dP^T buffer = {dS^T hi, dS^T lo}.
 __device__ __forceinline__ uint32_t bwd_pcol(int ks, int part = 0) { return static_cast<uint32_t>((ks >> 1) * 32 + (ks & 1) * 8 + part * 16); }
 
+// The issue helpers take the LOW WORDS of the operands' shared-memory descriptors (sdesc_lo) so
+// that every MMA costs one 32-bit add per operand in the issuing thread.
+
 // acc[128 keys x 64 queries] = A B^T with A = K or V tile, B = Q or dO block, both K-major (S^T and dP^T).
 template <class TR>
-__device__ __forceinline__ void bwd_issue_kmajor(uint32_t tmem_acc, uint32_t a_saddr, uint32_t b_saddr) {
+__device__ __forceinline__ void bwd_issue_kmajor(uint32_t tmem_acc, uint32_t a_lo, uint32_t b_lo) {
     if constexpr (!TR::SPLIT) {
 #pragma unroll
         for (int k = 0; k < TR::D / 16; ++k)
-            umma_ss_f16(tmem_acc, make_sdesc_sw128(a_saddr + (k / 4) * TR::KV_PANEL + (k % 4) * 32, 16, 1024),
-                        make_sdesc_sw128(b_saddr + (k / 4) * TR::Q_PANEL + (k % 4) * 32, 16, 1024), TR::IDESC_ST, k > 0);
+            umma_ss_f16(tmem_acc, sdesc_join(a_lo + (((k / 4) * TR::KV_PANEL + (k % 4) * 32) >> 4)),
+                        sdesc_join(b_lo + (((k / 4) * TR::Q_PANEL + (k % 4) * 32) >> 4)), TR::IDESC_ST, k > 0);
     } else {
 #pragma unroll
         for (int t = 0; t < 3; ++t)
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-                umma_ss_f16(tmem_acc, make_sdesc_sw128(a_saddr + split_a(t) * TR::KV_PANEL + k * 32, 16, 1024),
-                            make_sdesc_sw128(b_saddr + split_b(t) * TR::Q_PANEL + k * 32, 16, 1024), TR::IDESC_ST, (t | k) != 0);
+                umma_ss_f16(tmem_acc, sdesc_join(a_lo + ((split_a(t) * TR::KV_PANEL + k * 32) >> 4)),
+                            sdesc_join(b_lo + ((split_b(t) * TR::Q_PANEL + k * 32) >> 4)), TR::IDESC_ST, (t | k) != 0);
     }
 }
 
 // acc[128 keys x D] += A B with A = P^T or dS^T in TMEM (64 queries), B = dO or Q block, MN-major (dV and dK).
 template <class TR>
-__device__ __forceinline__ void bwd_issue_acc(uint32_t tmem_acc, uint32_t tmem_a, int part, uint32_t b_saddr, bool accumulate) {
+__device__ __forceinline__ void bwd_issue_acc(uint32_t tmem_acc, uint32_t tmem_a, int part, uint32_t b_lo_mn, bool accumulate) {
     if constexpr (!TR::SPLIT) {
 #pragma unroll
         for (int ks = 0; ks < TR::BQ / 16; ++ks)
-            umma_ts_f16(tmem_acc, tmem_a + bwd_pcol(ks, part), make_sdesc_sw128(b_saddr + ks * 2048, TR::Q_PANEL, 1024), TR::IDESC_DKV,
+            umma_ts_f16(tmem_acc, tmem_a + bwd_pcol(ks, part), sdesc_join(b_lo_mn + ((ks * 2048) >> 4)), TR::IDESC_DKV,
                         (accumulate || ks > 0) ? 1u : 0u);
     } else {
 #pragma unroll
@@ -127,26 +133,25 @@ __device__ __forceinline__ void bwd_issue_acc(uint32_t tmem_acc, uint32_t tmem_a
 #pragma unroll
             for (int ks = 0; ks < TR::BQ / 16; ++ks)
                 umma_ts_f16(tmem_acc, tmem_a + bwd_pcol(ks, split_a(t)),
-                            make_sdesc_sw128(b_saddr + split_b(t) * TR::Q_PANEL + ks * 2048, TR::Q_PANEL, 1024), TR::IDESC_DKV,
+                            sdesc_join(b_lo_mn + ((split_b(t) * TR::Q_PANEL + ks * 2048) >> 4)), TR::IDESC_DKV,
                             (accumulate || (t | ks) != 0) ? 1u : 0u);
     }
 }
 
 // acc[D x 64 queries] = K^T dS^T with K MN-major (M = head dim) and dS^T MN-major (N = queries).
 template <class TR>
-__device__ __forceinline__ void bwd_issue_dq(uint32_t tmem_acc, uint32_t k_saddr, uint32_t ds_saddr) {
+__device__ __forceinline__ void bwd_issue_dq(uint32_t tmem_acc, uint32_t k_lo_mn, uint32_t ds_lo) {
     if constexpr (!TR::SPLIT) {
 #pragma unroll
         for (int ks = 0; ks < TR::BKV / 16; ++ks)
-            umma_ss_f16(tmem_acc, make_sdesc_sw128(k_saddr + ks * 2048, TR::KV_PANEL, 1024),
-                        make_sdesc_sw128(ds_saddr + ks * 2048, 16, 1024), TR::IDESC_DQ, ks > 0);
+            umma_ss_f16(tmem_acc, sdesc_join(k_lo_mn + ((ks * 2048) >> 4)), sdesc_join(ds_lo + ((ks * 2048) >> 4)), TR::IDESC_DQ, ks > 0);
     } else {
 #pragma unroll
         for (int t = 0; t < 3; ++t)
 #pragma unroll
             for (int ks = 0; ks < TR::BKV / 16; ++ks)
-                umma_ss_f16(tmem_acc, make_sdesc_sw128(k_saddr + split_a(t) * TR::KV_PANEL + ks * 2048, TR::KV_PANEL, 1024),
-                            make_sdesc_sw128(ds_saddr + split_b(t) * TR::DS_PART + ks * 2048, 16, 1024), TR::IDESC_DQ, (t | ks) != 0);
+                umma_ss_f16(tmem_acc, sdesc_join(k_lo_mn + ((split_a(t) * TR::KV_PANEL + ks * 2048) >> 4)),
+                            sdesc_join(ds_lo + ((split_b(t) * TR::DS_PART + ks * 2048) >> 4)), TR::IDESC_DQ, (t | ks) != 0);
     }
 }
 
@@ -156,7 +161,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_k_lo,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_v_lo,
                 const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_do_lo,
-                const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv, BwdParams prm) {
+                const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
+                const __grid_constant__ CUtensorMap tm_dq, BwdParams prm) {
     constexpr int D = TR::D, BKV = TR::BKV, BQ = TR::BQ, NS = TR::NS;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -201,7 +207,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (warp == 13) { tmem_alloc(tmem_slot, TR::TM_COLS); tmem_relinquish(); }
     if (warp == 12 && lane == 0) {
         tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_do);
-        tma_prefetch_desc(&tm_dk); tma_prefetch_desc(&tm_dv);
+        tma_prefetch_desc(&tm_dk); tma_prefetch_desc(&tm_dv); tma_prefetch_desc(&tm_dq);
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -244,35 +250,40 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     } else if (warp == 13) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDS = smem_u32(sDS);
+            // descriptor low words: K-major views (lbo unused = 16) and MN-major views (lbo = panel stride)
+            const uint32_t lK = sdesc_lo(smem_u32(sK), 16), lV = sdesc_lo(smem_u32(sV), 16);
+            const uint32_t lK_mn = sdesc_lo(smem_u32(sK), TR::KV_PANEL), lDS = sdesc_lo(smem_u32(sDS), 16);
+            const uint32_t lQ0 = sdesc_lo(smem_u32(sQ), 16), lDO0 = sdesc_lo(smem_u32(sDO), 16);
+            constexpr uint32_t kStage = TR::Q_TILE >> 4;                               // ring stage stride in descriptor units
+            constexpr uint32_t kToMN = ((TR::Q_PANEL >> 4) << 16) - (1u << 16);        // K-major view -> MN-major view of a Q/dO stage
             mbar_wait(kv_full, 0, ab, 20);
             // S^T(blk) and dP^T(blk) into buffer blk & 1; the dP^T buffer must have been drained of dQ^T(blk - 2)
             auto issue_front = [&](int blk) {
                 const int b = blk & 1, s = blk % NS;
                 mbar_wait(&qdo_full[s], (blk / NS) & 1, ab, 21);
                 tc_fence_after_sync();
-                bwd_issue_kmajor<TR>(tmem + TR::TM_ST + b * 64, aK, smem_u32(sQ + s * TR::Q_TILE));
+                bwd_issue_kmajor<TR>(tmem + TR::TM_ST + b * 64, lK, lQ0 + s * kStage);
                 if (blk >= 2) { mbar_wait(&dq_empty[b], ((blk - 2) >> 1) & 1, ab, 24); tc_fence_after_sync(); }
-                bwd_issue_kmajor<TR>(tmem + TR::TM_DP + b * 64, aV, smem_u32(sDO + s * TR::Q_TILE));
+                bwd_issue_kmajor<TR>(tmem + TR::TM_DP + b * 64, lV, lDO0 + s * kStage);
                 umma_commit(&sdp_full[b]);
             };
             issue_front(0);
             if (nblk > 1) issue_front(1);
             for (int it = 0; it < nblk; ++it) {
                 const int b = it & 1, s = it % NS;
-                const uint32_t aQ = smem_u32(sQ + s * TR::Q_TILE), aDO = smem_u32(sDO + s * TR::Q_TILE);
+                const uint32_t lQ_mn = lQ0 + s * kStage + kToMN, lDO_mn = lDO0 + s * kStage + kToMN;
                 const uint32_t t_st = tmem + TR::TM_ST + b * 64, t_dp = tmem + TR::TM_DP + b * 64;
                 mbar_wait(&pds_full[b], (it >> 1) & 1, ab, 22);
                 tc_fence_after_sync();
                 if constexpr (!TR::SPLIT) {
-                    bwd_issue_dq<TR>(t_dp, aK, aDS);                            // dQ^T(it) over the consumed dP^T buffer
+                    bwd_issue_dq<TR>(t_dp, lK_mn, lDS);                            // dQ^T(it) over the consumed dP^T buffer
                     umma_commit(&dq_full[b]);
-                    bwd_issue_acc<TR>(tmem + TR::TM_DK, t_st, 1, aQ, it > 0);   // dK += dS^T Q
-                    bwd_issue_acc<TR>(tmem + TR::TM_DV, t_st, 0, aDO, it > 0);  // dV += P^T dO
+                    bwd_issue_acc<TR>(tmem + TR::TM_DK, t_st, 1, lQ_mn, it > 0);   // dK += dS^T Q
+                    bwd_issue_acc<TR>(tmem + TR::TM_DV, t_st, 0, lDO_mn, it > 0);  // dV += P^T dO
                 } else {
-                    bwd_issue_acc<TR>(tmem + TR::TM_DV, t_st, 0, aDO, it > 0);
-                    bwd_issue_acc<TR>(tmem + TR::TM_DK, t_dp, 0, aQ, it > 0);
-                    bwd_issue_dq<TR>(t_dp, aK, aDS);
+                    bwd_issue_acc<TR>(tmem + TR::TM_DV, t_st, 0, lDO_mn, it > 0);
+                    bwd_issue_acc<TR>(tmem + TR::TM_DK, t_dp, 0, lQ_mn, it > 0);
+                    bwd_issue_dq<TR>(t_dp, lK_mn, lDS);
                     umma_commit(&dq_full[b]);
                 }
                 umma_commit(&qdo_empty[s]);
@@ -413,6 +424,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // M = D rows of dQ^T: D=128 fills all lanes; D=64 uses lanes 0-15 of each quarter
         const int d = (D == 128) ? (wq * 32 + lane) : (wq * 16 + lane);
         const bool lane_ok = (D == 128) || (lane < 16);
+        float* stage = reinterpret_cast<float*>(smem + TR::OFF_DQ);
+        const bool issuer = (tid == 256);
         for (int it = 0; it < nblk; ++it) {
             const int b = it & 1, m = m0 + it;
             mbar_wait(&dq_full[b], (it >> 1) & 1, ab, 40);
@@ -424,24 +437,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&dq_empty[b]);
+            // the previous block's reduction must have finished reading the staging tile
+            if (issuer) tma_store_wait_read_all();
+            asm volatile("bar.sync 3, 128;" ::: "memory");
             if (lane_ok) {
-                float* base = prm.dq_acc + (static_cast<size_t>(bh) * T + static_cast<size_t>(m) * BQ) * D + d;
-                const int rows = min(BQ, T - m * BQ);
-                if (rows == BQ) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) atomicAdd(base + e * D, __uint_as_float(r0[e]));
+                for (int e = 0; e < 32; ++e) stage[e * D + d] = __uint_as_float(r0[e]);
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) atomicAdd(base + (32 + e) * D, __uint_as_float(r1[e]));
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e)
-                        if (e < rows) atomicAdd(base + e * D, __uint_as_float(r0[e]));
-#pragma unroll
-                    for (int e = 0; e < 32; ++e)
-                        if (32 + e < rows) atomicAdd(base + (32 + e) * D, __uint_as_float(r1[e]));
-                }
+                for (int e = 0; e < 32; ++e) stage[(32 + e) * D + d] = __uint_as_float(r1[e]);
+            }
+            fence_proxy_async_smem();
+            asm volatile("bar.sync 3, 128;" ::: "memory");
+            if (issuer) {
+                tma_reduce_add_3d(&tm_dq, stage, 0, m * BQ, bh);    // rows past T are clipped
+                tma_store_commit();
             }
         }
+        if (issuer) tma_store_wait_all();
     }
 
     // ------------------------------ tear-down ------------------------------

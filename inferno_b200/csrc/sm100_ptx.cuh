@@ -58,16 +58,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Returns false if the wait was abandoned (abort already raised, or limit hit).
+// The CTA abort flag lives in shared memory; it is polled only every 64th failed try so that
+// spinning warps do not load the shared-memory pipe the MMAs and compute warps depend on.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ab, int site) {
     if (mbar_try_wait(bar, parity)) return true;
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (*ab.cta_flag != 0) return false;
-        if (++spins > kSpinLimit) {
-            *ab.cta_flag = 1;
-            if (ab.status) atomicCAS(ab.status, 0, kDevTimeoutBase + site);
-            return false;
+        if ((++spins & 63u) == 0) {
+            if (*ab.cta_flag != 0) return false;
+            if (spins > kSpinLimit) {
+                *ab.cta_flag = 1;
+                if (ab.status) atomicCAS(ab.status, 0, kDevTimeoutBase + site);
+                return false;
+            }
         }
     }
 }
@@ -108,6 +112,13 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_sr
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2) {
     asm volatile(
         "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+// 3-D tile reduction shared -> global: global[tile] += shared[tile], element type from the tensor map.
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
         ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
@@ -191,6 +202,19 @@ __device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t saddr, uint32_t lb
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= static_cast<uint64_t>(1) << 46;   // descriptor version for sm_100
     d |= static_cast<uint64_t>(2) << 61;   // SWIZZLE_128B
+    return d;
+}
+
+// The same descriptor split into words, so that an MMA issue loop pays one 32-bit add per operand:
+// the high word is a constant for every 128B-swizzled operand with 1024-byte 8-row groups, and the
+// low word is (address >> 4) | (lbo >> 4) << 16, to which a byte offset adds as (offset >> 4).
+constexpr uint32_t kSdescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t sdesc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+    return ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+__device__ __forceinline__ uint64_t sdesc_join(uint32_t lo) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(kSdescHiSw128));
     return d;
 }
 
