@@ -38,7 +38,8 @@ typedef enum {
     IB200_ERR_WORKSPACE = 4,        /* workspace missing or smaller than ib200_attn_workspace_bytes */
     IB200_ERR_CUDA = 5,             /* a CUDA runtime/driver call failed (see ib200_last_cuda_error) */
     IB200_ERR_DEVICE_TIMEOUT = 6,   /* a bounded device-side wait expired; outputs are invalid */
-    IB200_ERR_NO_DEVICE = 7         /* no sm_100 device is current */
+    IB200_ERR_NO_DEVICE = 7,        /* no sm_100 device is current */
+    IB200_ERR_TOO_LARGE = 8         /* problem needs more scratch than the built-in static buffer holds */
 } ib200_status;
 
 enum { IB200_DTYPE_F32 = 0, IB200_DTYPE_BF16 = 1 };
@@ -72,6 +73,33 @@ int ib200_attn_bwd(const void* q, const void* k, const void* v, const void* o, c
                    const float* lse, void* dq, void* dk, void* dv,
                    int B, int H, int T, int D, float scale, int causal, int dtype, int math_mode,
                    void* workspace, size_t workspace_bytes, ib200_stream_t stream);
+
+/* Capacity in bytes of the scratch buffer that is compiled into the library for
+ * ib200_attn_bwd_static (one copy lives in the memory of every GPU that loads the library,
+ * from load until the process exits). */
+#define IB200_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+
+/* Backward pass for callers that have no way to hand over scratch memory at call time: code that
+ * runs where device allocation is off limits (a latency-critical loop that must never touch the
+ * allocator, a host application whose memory pool already owns the whole GPU and offers no hook to
+ * borrow from it), so that even the caller-owned workspace of ib200_attn_bwd cannot be provided.
+ * Same arguments, results and tolerances as ib200_attn_bwd minus the workspace pair: the dQ
+ * accumulator, the per-row vectors and (fp32 I/O) the operand copies live in a fixed buffer of
+ * IB200_STATIC_SCRATCH_BYTES inside the library, and the call allocates nothing on host or device.
+ *   - A problem whose scratch (what ib200_attn_workspace_bytes reports for IB200_PASS_BWD) exceeds
+ *     the buffer is refused with IB200_ERR_TOO_LARGE; nothing is launched.
+ *   - The first call on each device looks up the buffer's device address (a one-time set-up step);
+ *     make that first call outside any stream capture.
+ *   - All calls on a device share the one buffer, which still holds the previous call's contents
+ *     when the next begins; the parts that must start from zero are cleared on `stream` by each
+ *     call.  Two calls whose kernels may overlap on the GPU (different streams without an ordering
+ *     between them) race on it: serialise them.
+ *   - ib200_attn_check cannot be used with this entry point (the buffer is not caller-visible).
+ * This entry point has no counterpart in the reference. */
+int ib200_attn_bwd_static(const void* q, const void* k, const void* v, const void* o, const void* dO,
+                          const float* lse, void* dq, void* dk, void* dv,
+                          int B, int H, int T, int D, float scale, int causal, int dtype, int math_mode,
+                          ib200_stream_t stream);
 
 /* Synchronises `stream`, then reads the device status word that the kernels of the
  * last call using `workspace` left behind.  Returns IB200_OK, IB200_ERR_DEVICE_TIMEOUT

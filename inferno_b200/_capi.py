@@ -11,14 +11,15 @@ import os
 from . import build as _build
 
 OK = 0
-ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_MISALIGNED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE = range(1, 8)
+ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_MISALIGNED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE = range(1, 9)
+STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 DTYPE_F32, DTYPE_BF16 = 0, 1
 MATH_TF32, MATH_3XTF32 = 0, 1
 PASS_FWD, PASS_BWD = 0, 1
 
 EXPORTS = (
     "ib200_attn_workspace_bytes", "ib200_attn_fwd", "ib200_attn_bwd", "ib200_attn_check",
-    "ib200_status_string", "ib200_last_cuda_error", "ib200_version", "ib200_attn_set_timing_events",
+    "ib200_status_string", "ib200_last_cuda_error", "ib200_version", "ib200_attn_set_timing_events", "ib200_attn_bwd_static",
 )
 
 _lib = None
@@ -45,6 +46,8 @@ def lib() -> ctypes.CDLL:
         L.ib200_attn_fwd.restype = i
         L.ib200_attn_bwd.argtypes = [vp] * 9 + [i, i, i, i, f, i, i, i, vp, sz, vp]
         L.ib200_attn_bwd.restype = i
+        L.ib200_attn_bwd_static.argtypes = [vp] * 9 + [i, i, i, i, f, i, i, i, vp]
+        L.ib200_attn_bwd_static.restype = i
         L.ib200_attn_check.argtypes = [vp, vp, ctypes.POINTER(i)]
         L.ib200_attn_check.restype = i
         L.ib200_attn_set_timing_events.argtypes = [vp, vp, vp, vp]

@@ -211,6 +211,28 @@ int launch_bwd_all(const void* q, const void* k, const void* v, const void* o, c
     return launch_dq_finish<false>(dq_acc, dq, scale, N, stream);
 }
 
+// Scratch for ib200_attn_bwd_static.  In host code this name is only a handle for the runtime; the
+// device address is looked up once per device with cudaGetSymbolAddress and that pointer is what
+// the launch path receives.
+static __device__ __align__(256) unsigned char g_static_scratch[IB200_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};
+
+// Device address of the static scratch on the current device (set-up on first use per device).
+int static_scratch(void** out) {
+    int dev = 0;
+    if (!cuda_ok(cudaGetDevice(&dev))) return IB200_ERR_NO_DEVICE;
+    if (dev < 0 || dev >= kMaxDevices) return IB200_ERR_UNSUPPORTED;
+    if (!g_static_scratch_addr[dev]) {
+        void* p = nullptr;
+        if (!cuda_ok(cudaGetSymbolAddress(&p, g_static_scratch)) || !p) return IB200_ERR_CUDA;
+        g_static_scratch_addr[dev] = p;
+    }
+    *out = g_static_scratch_addr[dev];
+    return IB200_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -237,6 +259,7 @@ const char* ib200_status_string(int status) {
         case IB200_ERR_CUDA: return "CUDA call failed";
         case IB200_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
         case IB200_ERR_NO_DEVICE: return "no sm_100 device is current";
+        case IB200_ERR_TOO_LARGE: return "problem exceeds the capacity of the built-in static scratch buffer";
         default: return "unknown status";
     }
 }
@@ -306,6 +329,32 @@ int ib200_attn_bwd(const void* q, const void* k, const void* v, const void* o, c
     if (rc != IB200_OK) return rc;
     return launch_bwd_all(q, k, v, o, dO, lse, dq, dk, dv, BH, T, D, scale, causal, f32,
                           static_cast<uint8_t*>(workspace), stream);
+}
+
+int ib200_attn_bwd_static(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
+                          void* dq, void* dk, void* dv, int B, int H, int T, int D, float scale, int causal, int dtype,
+                          int math_mode, ib200_stream_t stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (!q || !k || !v || !o || !dO || !lse || !dq || !dk || !dv) return IB200_ERR_INVALID_ARGUMENT;
+    int rc = check_common(B, H, T, D, dtype, math_mode, causal);
+    if (rc != IB200_OK) return rc;
+    if (!(scale > 0.f) || !isfinite(scale)) return IB200_ERR_INVALID_ARGUMENT;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dO) || !aligned16(lse) ||
+        !aligned16(dq) || !aligned16(dk) || !aligned16(dv))
+        return IB200_ERR_MISALIGNED;
+    const long BH = static_cast<long>(B) * H;
+    const long N = BH * T * D;
+    const bool f32 = dtype == IB200_DTYPE_F32;
+    if (bwd_ws_bytes(N, BH, T, f32) > static_cast<size_t>(IB200_STATIC_SCRATCH_BYTES)) return IB200_ERR_TOO_LARGE;
+    rc = device_ok();
+    if (rc != IB200_OK) return rc;
+    void* scratch = nullptr;
+    rc = static_scratch(&scratch);
+    if (rc != IB200_OK) return rc;
+    // launch_bwd_all clears the header and the dQ accumulator on `stream` and rewrites every other
+    // part of the scratch it reads, so stale contents of an earlier call are never consumed
+    return launch_bwd_all(q, k, v, o, dO, lse, dq, dk, dv, BH, T, D, scale, causal, f32,
+                          static_cast<uint8_t*>(scratch), stream);
 }
 
 int ib200_attn_check(const void* workspace, ib200_stream_t stream_, int* device_code) {
