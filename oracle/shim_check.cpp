@@ -1,0 +1,57 @@
+// TEST INFRASTRUCTURE ONLY.  Proves that the fused op drops into the reference: it is compiled against
+// the reference's own headers and objects, run on Device::cuda(0), and its gradients are produced by the
+// reference's autograd Engine walking the AttentionBackward node (seeded through a multiply, because
+// Engine::backward always seeds ones, src/inferno/gradengine/engine.cpp:59).
+// Usage: shim_check B H T D q.bin k.bin v.bin do.bin out_prefix   -> writes <prefix>.{o,dq,dk,dv}.bin
+#include <cstdio>
+#include <cstdlib>
+#include <string>
+#include <vector>
+
+#include <inferno/inferno.h>
+#include "inferno/core/ops_impl.h"
+#include "inferno/core/tensorimpl.h"
+
+#include "../inferno_b200/inferno_shim/causal_attention.h"
+
+using Inferno::Tensor;
+
+static std::vector<float> read_bin(const char* path, size_t n) {
+    std::vector<float> v(n);
+    FILE* f = std::fopen(path, "rb");
+    if (!f || std::fread(v.data(), sizeof(float), n, f) != n) { std::fprintf(stderr, "cannot read %s\n", path); std::exit(2); }
+    std::fclose(f);
+    return v;
+}
+static void write_tensor(const std::string& path, const Tensor& t_in, size_t n) {
+    Tensor t = t_in.contiguous().to(Inferno::Device::cpu());
+    const float* p = Inferno::GetImpl(t)->data_as_ptr<float>() + t.offset();
+    FILE* f = std::fopen(path.c_str(), "wb");
+    std::fwrite(p, sizeof(float), n, f);
+    std::fclose(f);
+}
+
+int main(int argc, char** argv) {
+    if (argc < 10) { std::fprintf(stderr, "usage: %s B H T D q k v do out_prefix\n", argv[0]); return 2; }
+    const size_t B = std::strtoul(argv[1], nullptr, 10), H = std::strtoul(argv[2], nullptr, 10);
+    const size_t T = std::strtoul(argv[3], nullptr, 10), D = std::strtoul(argv[4], nullptr, 10);
+    const size_t n = B * H * T * D;
+    const std::string prefix = argv[9];
+    Inferno::Device dev = Inferno::Device::cuda(0);
+    std::vector<float> hq = read_bin(argv[5], n), hk = read_bin(argv[6], n), hv = read_bin(argv[7], n), hdo = read_bin(argv[8], n);
+    Tensor q(Inferno::DType::Float32, hq, {B, H, T, D}, "q", dev, true);
+    Tensor k(Inferno::DType::Float32, hk, {B, H, T, D}, "k", dev, true);
+    Tensor v(Inferno::DType::Float32, hv, {B, H, T, D}, "v", dev, true);
+    Tensor dO(Inferno::DType::Float32, hdo, {B, H, T, D}, "dO", dev, false);
+
+    Tensor y = Inferno::causal_attention(q, k, v, 1.0f / std::sqrt(static_cast<float>(D)));
+    write_tensor(prefix + ".o.bin", y, n);
+    Tensor loss = y * dO;          // MultiplyBackward hands dO to AttentionBackward
+    loss.backward();
+    if (!q.grad() || !k.grad() || !v.grad()) { std::fprintf(stderr, "a gradient did not arrive\n"); return 3; }
+    write_tensor(prefix + ".dq.bin", q.Getgrad(), n);
+    write_tensor(prefix + ".dk.bin", k.Getgrad(), n);
+    write_tensor(prefix + ".dv.bin", v.Getgrad(), n);
+    std::printf("shim_check ok\n");
+    return 0;
+}
