@@ -70,40 +70,40 @@ constexpr float kRescaleLog2 = 8.0f;
 __device__ __forceinline__ constexpr int split_a(int t) { return t == 1 ? 1 : 0; }
 __device__ __forceinline__ constexpr int split_b(int t) { return t == 2 ? 1 : 0; }
 
+// The issue helpers take descriptor LOW WORDS (sdesc_lo) so that each MMA costs one 32-bit add per operand.
 template <class TR>
-__device__ __forceinline__ void fwd_issue_s(uint32_t tmem_s, uint32_t q_saddr, uint32_t k_saddr) {
+__device__ __forceinline__ void fwd_issue_s(uint32_t tmem_s, uint32_t q_lo, uint32_t k_lo) {
     if constexpr (!TR::SPLIT) {
 #pragma unroll
         for (int k = 0; k < TR::D / 16; ++k) {
-            const uint32_t off = (k / 4) * TR::PANEL_BYTES + (k % 4) * 32;
-            umma_ss_f16(tmem_s, make_sdesc_sw128(q_saddr + off, 16, 1024), make_sdesc_sw128(k_saddr + off, 16, 1024), TR::IDESC_S, k > 0);
+            const uint32_t off = ((k / 4) * TR::PANEL_BYTES + (k % 4) * 32) >> 4;
+            umma_ss_f16(tmem_s, sdesc_join(q_lo + off), sdesc_join(k_lo + off), TR::IDESC_S, k > 0);
         }
     } else {
 #pragma unroll
         for (int t = 0; t < 3; ++t)
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-                umma_ss_f16(tmem_s, make_sdesc_sw128(q_saddr + split_a(t) * TR::PANEL_BYTES + k * 32, 16, 1024),
-                            make_sdesc_sw128(k_saddr + split_b(t) * TR::PANEL_BYTES + k * 32, 16, 1024), TR::IDESC_S, (t | k) != 0);
+                umma_ss_f16(tmem_s, sdesc_join(q_lo + ((split_a(t) * TR::PANEL_BYTES + k * 32) >> 4)),
+                            sdesc_join(k_lo + ((split_b(t) * TR::PANEL_BYTES + k * 32) >> 4)), TR::IDESC_S, (t | k) != 0);
     }
 }
 
+// v_lo_mn: low word of V's MN-major view (lbo = panel stride).
 template <class TR>
-__device__ __forceinline__ void fwd_issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t v_saddr, bool first_tile) {
+__device__ __forceinline__ void fwd_issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t v_lo_mn, bool first_tile) {
     if constexpr (!TR::SPLIT) {
 #pragma unroll
         for (int k = 0; k < TR::PV_KSTEPS; ++k)
-            umma_ts_f16(tmem_o, tmem_p + k * 8, make_sdesc_sw128(v_saddr + k * 2048, TR::PANEL_BYTES, 1024), TR::IDESC_PV,
-                        (!first_tile || k > 0) ? 1u : 0u);
+            umma_ts_f16(tmem_o, tmem_p + k * 8, sdesc_join(v_lo_mn + ((k * 2048) >> 4)), TR::IDESC_PV, (!first_tile || k > 0) ? 1u : 0u);
     } else {
         // P_hi in columns 0-63, P_lo in columns 64-127 of the S region; V_hi / V_lo are the two panels
 #pragma unroll
         for (int t = 0; t < 3; ++t)
 #pragma unroll
             for (int k = 0; k < TR::PV_KSTEPS; ++k)
-                umma_ts_f16(tmem_o, tmem_p + split_a(t) * 64 + k * 8,
-                            make_sdesc_sw128(v_saddr + split_b(t) * TR::PANEL_BYTES + k * 2048, TR::PANEL_BYTES, 1024), TR::IDESC_PV,
-                            (!first_tile || (t | k) != 0) ? 1u : 0u);
+                umma_ts_f16(tmem_o, tmem_p + split_a(t) * 64 + k * 8, sdesc_join(v_lo_mn + ((split_b(t) * TR::PANEL_BYTES + k * 2048) >> 4)),
+                            TR::IDESC_PV, (!first_tile || (t | k) != 0) ? 1u : 0u);
     }
 }
 
@@ -163,7 +163,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
     // Register rebalancing between warpgroups (the launch gives every thread 168).
     if (warp >= 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     }
     if (warp == 9) {
         // ------------------------------ TMA producer ------------------------------
@@ -191,12 +191,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (lane == 0 && n_iter > 0) {
             const uint32_t tm_s[2] = {tmem + TR::TM_S0, tmem + TR::TM_S1};
             const uint32_t tm_oo[2] = {tmem + TR::TM_O0, tmem + TR::TM_O1};
-            const uint32_t q_addr[2] = {smem_u32(sQ), smem_u32(sQ + TR::TILE_BYTES)};
+            const uint32_t q_addr[2] = {sdesc_lo(smem_u32(sQ), 16), sdesc_lo(smem_u32(sQ + TR::TILE_BYTES), 16)};
+            const uint32_t k_lo0 = sdesc_lo(smem_u32(sK), 16), v_lo0 = sdesc_lo(smem_u32(sV), TR::PANEL_BYTES);
+            constexpr uint32_t kStage = TR::TILE_BYTES >> 4;
             mbar_wait(q_full, 0, ab, 20);
             mbar_wait(&k_full[0], 0, ab, 21);
             tc_fence_after_sync();
             for (int i = 0; i < 2; ++i)
-                if (n_kv[i] > 0) { fwd_issue_s<TR>(tm_s[i], q_addr[i], smem_u32(sK)); umma_commit(&s_full[i]); }
+                if (n_kv[i] > 0) { fwd_issue_s<TR>(tm_s[i], q_addr[i], k_lo0); umma_commit(&s_full[i]); }
             umma_commit(&k_empty[0]);
             for (int j = 0; j < n_iter; ++j) {
                 const int sv = j % KS;
@@ -208,10 +210,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     if (j < n_kv[i]) {
                         mbar_wait(&p_full[i], j & 1, ab, 24);
                         tc_fence_after_sync();
-                        fwd_issue_pv<TR>(tm_oo[i], tm_s[i], smem_u32(sV + sv * TR::TILE_BYTES), j == 0);
+                        fwd_issue_pv<TR>(tm_oo[i], tm_s[i], v_lo0 + sv * kStage, j == 0);
                         umma_commit(&o_full[i]);
                         if (j + 1 < n_kv[i]) {
-                            fwd_issue_s<TR>(tm_s[i], q_addr[i], smem_u32(sK + sk_next * TR::TILE_BYTES));
+                            fwd_issue_s<TR>(tm_s[i], q_addr[i], k_lo0 + sk_next * kStage);
                             umma_commit(&s_full[i]);
                         }
                     }
@@ -222,7 +224,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
     } else if (warp < 8) {
         // ------------------------------ softmax groups ------------------------------
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         const int i = warp >> 2;                 // query tile handled by this group
         const int t = tid & 127;                 // row inside the tile
         const int wq = warp & 3;                 // TMEM lane quarter
@@ -256,9 +258,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 for (int e = 0; e < BN; ++e)
                     if (col0 + e > limit) s[e] = -INFINITY;
             }
-            float mx = s[0];
+            // row maximum: eight independent chains (a single 127-deep chain would expose its full latency)
+            float mx8[8];
 #pragma unroll
-            for (int e = 1; e < BN; ++e) mx = fmaxf(mx, s[e]);
+            for (int e = 0; e < 8; ++e) mx8[e] = s[e];
+#pragma unroll
+            for (int e = 8; e < BN; e += 8)
+#pragma unroll
+                for (int u = 0; u < 8; ++u) mx8[u] = fmaxf(mx8[u], s[e + u]);
+            const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             float mx_s = mx * c;
             if (mx == -INFINITY) mx_s = m_used;                    // fully masked row in this tile
             if (j == 0) {
@@ -282,15 +290,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     tmem_wait_st();
                 }
             }
-            float lsum = 0.f;
+            // P = exp2(s * c - m): packed fp32x2 FMA, row sum in four independent packed accumulators
+            const uint64_t c2 = pack_f32x2(c, c), nm2 = pack_f32x2(-m_used, -m_used);
+            uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
             for (int cc = 0; cc < BN; cc += 32) {
                 uint32_t pk[16], pl[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
-                    const float p0 = fast_exp2(fmaf(s[cc + e], c, -m_used));
-                    const float p1 = fast_exp2(fmaf(s[cc + e + 1], c, -m_used));
-                    lsum += p0 + p1;
+                    float x0, x1;
+                    unpack_f32x2(ffma2(pack_f32x2(s[cc + e], s[cc + e + 1]), c2, nm2), x0, x1);
+                    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                    acc2[(e >> 1) & 3] = fadd2(acc2[(e >> 1) & 3], pack_f32x2(p0, p1));
                     const uint32_t hi = pack_bf16x2(p0, p1);
                     pk[e >> 1] = hi;
                     if constexpr (TR::SPLIT)
@@ -298,6 +309,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 }
                 tmem_st_x16(tm_s + (cc >> 1), pk);
                 if constexpr (TR::SPLIT) tmem_st_x16(tm_s + 64 + (cc >> 1), pl);
+            }
+            float lsum;
+            {
+                float a0, a1;
+                unpack_f32x2(fadd2(fadd2(acc2[0], acc2[1]), fadd2(acc2[2], acc2[3])), a0, a1);
+                lsum = a0 + a1;
             }
             l += lsum;
             tmem_wait_st();
