@@ -74,6 +74,32 @@ int ib200_attn_bwd(const void* q, const void* k, const void* v, const void* o, c
                    int B, int H, int T, int D, float scale, int causal, int dtype, int math_mode,
                    void* workspace, size_t workspace_bytes, ib200_stream_t stream);
 
+/* Strided operands.  Element strides of the batch, head and token axes of one [B, H, T, D] operand; the D
+ * elements of a row must be contiguous, every stride a multiple of 16 bytes, the base 16-byte aligned.
+ * Dense row-major is {H*T*D, T*D, D}.  A q / k / v slice of the packed projection output [B, T, 3, H, D]
+ * (the reference's qkv = Wqkv(x), InfernoApp/main.cpp:712) is {T*3*H*D, D, 3*H*D}; an output written straight
+ * into [B, T, H, D] (what main.cpp:758-761 obtains with transpose + contiguous + reshape) is {T*H*D, D, H*D}. */
+typedef struct {
+    int64_t stride_b, stride_h, stride_t;
+} ib200_layout;
+
+/* ib200_attn_fwd / ib200_attn_bwd for operands that live inside larger buffers: same semantics, workspace and
+ * statuses; each tensor carries its own layout (NULL = dense).  lse stays dense [B, H, T].  These take the
+ * place of the reference's layout plumbing around attention -- slice + contiguous (x3), reshape,
+ * transpose(1,2).contiguous() (x3), k^T contiguous, and transpose + contiguous on the way out
+ * (InfernoApp/main.cpp:716-737, 758-761; SliceBackward's scatter-adds, src/inferno/gradfn/slicebackward.cpp:35-53,
+ * on the way back): the TMA descriptors absorb the strides, so no copy kernel runs. */
+int ib200_attn_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse,
+                           const ib200_layout* lq, const ib200_layout* lk, const ib200_layout* lv, const ib200_layout* lo,
+                           int B, int H, int T, int D, float scale, int causal, int dtype, int math_mode,
+                           void* workspace, size_t workspace_bytes, ib200_stream_t stream);
+int ib200_attn_bwd_strided(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
+                           void* dq, void* dk, void* dv,
+                           const ib200_layout* lq, const ib200_layout* lk, const ib200_layout* lv, const ib200_layout* lo,
+                           const ib200_layout* ldo, const ib200_layout* ldq, const ib200_layout* ldk, const ib200_layout* ldv,
+                           int B, int H, int T, int D, float scale, int causal, int dtype, int math_mode,
+                           void* workspace, size_t workspace_bytes, ib200_stream_t stream);
+
 /* Capacity in bytes of the scratch buffer that is compiled into the library for
  * ib200_attn_bwd_static (one copy lives in the memory of every GPU that loads the library,
  * from load until the process exits). */

@@ -19,8 +19,15 @@ PASS_FWD, PASS_BWD = 0, 1
 
 EXPORTS = (
     "ib200_attn_workspace_bytes", "ib200_attn_fwd", "ib200_attn_bwd", "ib200_attn_check",
-    "ib200_status_string", "ib200_last_cuda_error", "ib200_version", "ib200_attn_set_timing_events", "ib200_attn_bwd_static",
+    "ib200_status_string", "ib200_last_cuda_error", "ib200_version", "ib200_attn_set_timing_events", "ib200_attn_bwd_static", "ib200_attn_fwd_strided", "ib200_attn_bwd_strided",
 )
+
+
+
+class Layout(ctypes.Structure):
+    """``ib200_layout``: element strides of the batch, head and token axes of a [B, H, T, D] operand."""
+    _fields_ = [("stride_b", ctypes.c_int64), ("stride_h", ctypes.c_int64), ("stride_t", ctypes.c_int64)]
+
 
 _lib = None
 
@@ -28,7 +35,8 @@ _lib = None
 class Ib200Error(RuntimeError):
     def __init__(self, status: int, where: str):
         self.status = status
-        super().__init__(f"{where}: {status_string(status)} (status {status})")
+        detail = f", cudaError {lib().ib200_last_cuda_error()}" if status == ERR_CUDA else ""
+        super().__init__(f"{where}: {status_string(status)} (status {status}{detail})")
 
 
 def lib() -> ctypes.CDLL:
@@ -46,6 +54,11 @@ def lib() -> ctypes.CDLL:
         L.ib200_attn_fwd.restype = i
         L.ib200_attn_bwd.argtypes = [vp] * 9 + [i, i, i, i, f, i, i, i, vp, sz, vp]
         L.ib200_attn_bwd.restype = i
+        lp = ctypes.POINTER(Layout)
+        L.ib200_attn_fwd_strided.argtypes = [vp, vp, vp, vp, vp, lp, lp, lp, lp, i, i, i, i, f, i, i, i, vp, sz, vp]
+        L.ib200_attn_fwd_strided.restype = i
+        L.ib200_attn_bwd_strided.argtypes = [vp] * 9 + [lp] * 8 + [i, i, i, i, f, i, i, i, vp, sz, vp]
+        L.ib200_attn_bwd_strided.restype = i
         L.ib200_attn_bwd_static.argtypes = [vp] * 9 + [i, i, i, i, f, i, i, i, vp]
         L.ib200_attn_bwd_static.restype = i
         L.ib200_attn_check.argtypes = [vp, vp, ctypes.POINTER(i)]

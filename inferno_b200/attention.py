@@ -58,6 +58,27 @@ def _check_inputs(*tensors: torch.Tensor):
     return q.shape
 
 
+def _layout(t: torch.Tensor) -> _capi.Layout:
+    """Strides of a [B, H, T, D] tensor (any view whose last axis is contiguous) for the strided entry points."""
+    if t.stride(3) != 1:
+        raise ValueError("causal_attention: the head-dim axis must be contiguous")
+    return _capi.Layout(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _dense_or_view(t: torch.Tensor) -> torch.Tensor:
+    """Use the tensor in place when the kernels can address it (contiguous rows, 16-byte aligned strides);
+    otherwise make the dense copy the reference makes with .contiguous()."""
+    unit = 16 // t.element_size()
+    ok = t.stride(3) == 1 and all(t.stride(a) % unit == 0 and t.stride(a) > 0 for a in (0, 1, 2)) and t.data_ptr() % 16 == 0
+    return t if ok else t.contiguous()
+
+
+def empty_bthd(B: int, H: int, T: int, D: int, dtype, device) -> torch.Tensor:
+    """A [B, H, T, D] view over [B, T, H, D] memory: what the attention output must look like for
+    ``y.transpose(1, 2).reshape(B, T, C)`` to be free (InfernoApp/main.cpp:758-761 pays a copy for it)."""
+    return torch.empty((B, T, H, D), dtype=dtype, device=device).transpose(1, 2)
+
+
 def _raise(rc: int, where: str):
     if rc != _capi.OK:
         raise _capi.Ib200Error(rc, where)
@@ -65,44 +86,51 @@ def _raise(rc: int, where: str):
 
 def attention_forward(q, k, v, scale: float | None = None, causal: bool = True, math_mode: int = _capi.MATH_TF32,
                       out=None, lse=None):
-    """Launch the forward kernel.  Returns (o [B,H,T,D], lse [B,H,T] fp32).  Asynchronous on the current stream."""
+    """Launch the forward kernel.  Returns (o [B,H,T,D], lse [B,H,T] fp32).  Asynchronous on the current stream.
+
+    q, k, v (and ``out``) may be arbitrary [B,H,T,D] views with a contiguous last axis -- e.g. slices of a packed
+    [B,T,3,H,D] projection, or an output laid out [B,T,H,D] -- and are then read and written in place."""
     B, H, T, D = _check_inputs(q, k, v)
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    q, k, v = _dense_or_view(q), _dense_or_view(k), _dense_or_view(v)
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     dt = _DTYPES[q.dtype]
-    o = torch.empty_like(q) if out is None else out
+    o = torch.empty((B, H, T, D), dtype=q.dtype, device=q.device) if out is None else out
     if lse is None:
         lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
     ws = _workspace.get(_capi.workspace_bytes(B, H, T, D, dt, _capi.PASS_FWD), q.device)
+    lq, lk, lv, lo = _layout(q), _layout(k), _layout(v), _layout(o)
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
-        rc = _capi.lib().ib200_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
-                                        B, H, T, D, float(scale), int(bool(causal)), dt, int(math_mode),
-                                        ws.data_ptr(), ws.numel(), stream)
-    _raise(rc, "ib200_attn_fwd")
+        rc = _capi.lib().ib200_attn_fwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                                lq, lk, lv, lo, B, H, T, D, float(scale), int(bool(causal)), dt, int(math_mode),
+                                                ws.data_ptr(), ws.numel(), stream)
+    _raise(rc, "ib200_attn_fwd_strided")
     return o, lse
 
 
 def attention_backward(q, k, v, o, dO, lse, scale: float | None = None, causal: bool = True,
                        math_mode: int = _capi.MATH_TF32, dq=None, dk=None, dv=None):
-    """Launch the backward kernels.  Returns (dq, dk, dv).  Asynchronous on the current stream."""
+    """Launch the backward kernels.  Returns (dq, dk, dv).  Asynchronous on the current stream.
+    Operands and outputs may be strided views as in ``attention_forward``."""
     B, H, T, D = _check_inputs(q, k, v, o, dO)
-    q, k, v, o, dO = (t.contiguous() for t in (q, k, v, o, dO))
+    q, k, v, o, dO = (_dense_or_view(t) for t in (q, k, v, o, dO))
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     dt = _DTYPES[q.dtype]
-    dq = torch.empty_like(q) if dq is None else dq
-    dk = torch.empty_like(q) if dk is None else dk
-    dv = torch.empty_like(q) if dv is None else dv
+    mk = lambda: torch.empty((B, H, T, D), dtype=q.dtype, device=q.device)
+    dq = mk() if dq is None else dq
+    dk = mk() if dk is None else dk
+    dv = mk() if dv is None else dv
     ws = _workspace.get(_capi.workspace_bytes(B, H, T, D, dt, _capi.PASS_BWD), q.device)
+    lays = [_layout(t) for t in (q, k, v, o, dO, dq, dk, dv)]
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
-        rc = _capi.lib().ib200_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dO.data_ptr(),
-                                        lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                        B, H, T, D, float(scale), int(bool(causal)), dt, int(math_mode),
-                                        ws.data_ptr(), ws.numel(), stream)
-    _raise(rc, "ib200_attn_bwd")
+        rc = _capi.lib().ib200_attn_bwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dO.data_ptr(),
+                                                lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), *lays,
+                                                B, H, T, D, float(scale), int(bool(causal)), dt, int(math_mode),
+                                                ws.data_ptr(), ws.numel(), stream)
+    _raise(rc, "ib200_attn_bwd_strided")
     return dq, dk, dv
 
 
@@ -140,11 +168,16 @@ class AttentionBackward(torch.autograd.Function):
 
     Plays the role a ``class AttentionBackward : public Node`` would in the reference
     (src/inferno/gradfn/node.h:23-45: ``backward()``, ``release()``, ``get_inputs()``).
+    With ``bthd_out`` the output is laid out [B,T,H,D] in memory (returned as a [B,H,T,D] view).  When q, k, v are
+    slices of one packed [B,T,3,H,D] buffer the gradients are written into one packed buffer of the same layout,
+    so that autograd's accumulation into the projection's gradient needs no scatter-add.
     """
 
     @staticmethod
-    def forward(ctx, q, k, v, scale, causal, math_mode):
-        o, lse = attention_forward(q, k, v, scale, causal, math_mode)
+    def forward(ctx, q, k, v, scale, causal, math_mode, bthd_out):
+        B, H, T, D = q.shape
+        out = empty_bthd(B, H, T, D, q.dtype, q.device) if bthd_out else None
+        o, lse = attention_forward(q, k, v, scale, causal, math_mode, out=out)
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.scale, ctx.causal, ctx.math_mode = scale, causal, math_mode
         return o
@@ -152,13 +185,35 @@ class AttentionBackward(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dO):
         q, k, v, o, lse = ctx.saved_tensors
-        dq, dk, dv = attention_backward(q, k, v, o, dO, lse, ctx.scale, ctx.causal, ctx.math_mode)
-        return dq, dk, dv, None, None, None
+        B, H, T, D = q.shape
+        packed = (q.stride() == k.stride() == v.stride() and q.stride(2) == 3 * H * D and q.stride(1) == D and
+                  k.data_ptr() - q.data_ptr() == H * D * q.element_size() and v.data_ptr() - k.data_ptr() == H * D * q.element_size())
+        if packed:
+            g = torch.empty((B, T, 3, H, D), dtype=q.dtype, device=q.device)
+            dq, dk, dv = (g[:, :, i].transpose(1, 2) for i in range(3))
+            attention_backward(q, k, v, o, dO, lse, ctx.scale, ctx.causal, ctx.math_mode, dq=dq, dk=dk, dv=dv)
+        else:
+            dq, dk, dv = attention_backward(q, k, v, o, dO, lse, ctx.scale, ctx.causal, ctx.math_mode)
+        return dq, dk, dv, None, None, None, None
 
 
 def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float | None = None,
-                     math_mode: int = _capi.MATH_TF32) -> torch.Tensor:
-    """``softmax(mask(q k^T * scale)) v`` with a causal mask; differentiable."""
+                     math_mode: int = _capi.MATH_TF32, bthd_out: bool = False) -> torch.Tensor:
+    """``softmax(mask(q k^T * scale)) v`` with a causal mask; differentiable.  q, k, v: [B,H,T,D] tensors or views."""
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
-    return AttentionBackward.apply(q, k, v, float(scale), True, int(math_mode))
+    return AttentionBackward.apply(q, k, v, float(scale), True, int(math_mode), bool(bthd_out))
+
+
+def causal_attention_packed(qkv: torch.Tensor, num_heads: int, scale: float | None = None,
+                            math_mode: int = _capi.MATH_TF32) -> torch.Tensor:
+    """Attention straight on the fused projection output: ``qkv`` is [B, T, 3*C] (= [B,T,3,H,D]); returns [B, T, C].
+    Replaces slice / contiguous / reshape / transpose / contiguous before the kernels and transpose / contiguous /
+    reshape after them (InfernoApp/main.cpp:716-737, 758-761) with stride arithmetic: no copy kernel runs."""
+    B, T, C3 = qkv.shape
+    C = C3 // 3
+    D = C // num_heads
+    packed = qkv.view(B, T, 3, num_heads, D)
+    q, k, v = (packed[:, :, i].transpose(1, 2) for i in range(3))      # [B,H,T,D] views
+    y = causal_attention(q, k, v, scale, math_mode, bthd_out=True)      # [B,H,T,D] view over [B,T,H,D] memory
+    return y.transpose(1, 2).reshape(B, T, C)

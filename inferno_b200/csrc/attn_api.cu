@@ -17,6 +17,15 @@ using namespace ib200;
 thread_local int g_last_cuda_error = 0;
 thread_local cudaEvent_t g_ev[4] = {nullptr, nullptr, nullptr, nullptr};   // fwd start/stop, bwd start/stop
 
+// Timing events are an observability aid: a handle that has gone stale (the hook is per host thread and a
+// caller may have destroyed its events without switching the hook off on that thread) must not fail the launch.
+inline void record_timing_event(int which, cudaStream_t stream) {
+    if (g_ev[which] && cudaEventRecord(g_ev[which], stream) != cudaSuccess) {
+        (void)cudaGetLastError();
+        g_ev[which] = nullptr;
+    }
+}
+
 inline bool cuda_ok(cudaError_t e) {
     if (e == cudaSuccess) return true;
     g_last_cuda_error = static_cast<int>(e);
@@ -39,16 +48,19 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// Tensor map over a dense [BH, T, D] tensor; box = [box_rows x 128 bytes], 128B swizzle.
-bool make_tmap(CUtensorMap* m, const void* base, bool f32, int D, int T, long BH, int box_rows) {
+// Tensor map over a [B, H, T, D] operand with arbitrary batch / head / token strides, seen as the 4-D tensor
+// {D, T, H, B}; box = [box_rows x 128 bytes], 128B swizzle.  Rows past T are zero-filled on load and clipped
+// on store; a tile never crosses into another head.
+bool make_tmap(CUtensorMap* m, const void* base, bool f32, int D, int T, const RowLayout& L, long BH, int box_rows) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return false;
     const cuuint64_t es = f32 ? 4 : 2;
-    cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(BH)};
-    cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * es, static_cast<cuuint64_t>(T) * D * es};
-    cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(box_rows), 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = enc(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+    const long B = BH / L.H;
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(L.H), static_cast<cuuint64_t>(B)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(L.st) * es, static_cast<cuuint64_t>(L.sh) * es, static_cast<cuuint64_t>(L.sb) * es};
+    cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(box_rows), 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
                      const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
@@ -92,14 +104,15 @@ int device_ok() {
 
 template <class TR>
 int launch_fwd(const void* q, const void* q_lo, const void* k, const void* k_lo, const void* v, const void* v_lo, void* o,
+               const RowLayout& lq, const RowLayout& lk, const RowLayout& lv, const RowLayout& lo,
                float* lse, int* status, long BH, int T, float scale, int causal, cudaStream_t stream) {
     CUtensorMap tq, tql, tk, tkl, tv, tvl, to;
-    if (!make_tmap(&tq, q, false, TR::D, T, BH, 128) || !make_tmap(&tk, k, false, TR::D, T, BH, 128) ||
-        !make_tmap(&tv, v, false, TR::D, T, BH, 128) || !make_tmap(&to, o, TR::SPLIT, TR::D, T, BH, 128))
+    if (!make_tmap(&tq, q, false, TR::D, T, lq, BH, 128) || !make_tmap(&tk, k, false, TR::D, T, lk, BH, 128) ||
+        !make_tmap(&tv, v, false, TR::D, T, lv, BH, 128) || !make_tmap(&to, o, TR::SPLIT, TR::D, T, lo, BH, 128))
         return IB200_ERR_CUDA;
     if (TR::SPLIT) {
-        if (!make_tmap(&tql, q_lo, false, TR::D, T, BH, 128) || !make_tmap(&tkl, k_lo, false, TR::D, T, BH, 128) ||
-            !make_tmap(&tvl, v_lo, false, TR::D, T, BH, 128))
+        if (!make_tmap(&tql, q_lo, false, TR::D, T, lq, BH, 128) || !make_tmap(&tkl, k_lo, false, TR::D, T, lk, BH, 128) ||
+            !make_tmap(&tvl, v_lo, false, TR::D, T, lv, BH, 128))
             return IB200_ERR_CUDA;
     } else {
         tql = tq; tkl = tk; tvl = tv;
@@ -111,29 +124,32 @@ int launch_fwd(const void* q, const void* q_lo, const void* k, const void* k_lo,
     prm.status = status;
     prm.T = T;
     prm.BH = static_cast<int>(BH);
+    prm.H = lq.H;
     prm.causal = causal;
     prm.scale_log2 = scale * 1.4426950408889634f;
     const int pairs = (T + 255) / 256;
     if (BH > 65535) return IB200_ERR_UNSUPPORTED;
     dim3 grid(pairs, static_cast<unsigned>(BH), 1);
-    if (g_ev[0]) cudaEventRecord(g_ev[0], stream);
+    record_timing_event(0, stream);
     attn_fwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tql, tk, tkl, tv, tvl, to, prm);
-    if (g_ev[1]) cudaEventRecord(g_ev[1], stream);
-    return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
+    const bool launched = cuda_ok(cudaGetLastError());
+    record_timing_event(1, stream);
+    return launched ? IB200_OK : IB200_ERR_CUDA;
 }
 
 template <class TR>
 int launch_bwd(const void* const q[2], const void* const k[2], const void* const v[2], const void* const dO[2],
-               const float* nlse2, const float* ndelta, int T_pad, float* dq_acc, void* dk, void* dv, int* status, long BH, int T,
+               const RowLayout& lq, const RowLayout& lk, const RowLayout& lv, const RowLayout& ldo, const RowLayout& ldk,
+               const RowLayout& ldv, const float* nlse2, const float* ndelta, int T_pad, float* dq_acc, void* dk, void* dv, int* status, long BH, int T,
                float scale, int causal, cudaStream_t stream) {
     CUtensorMap tq[2], tk[2], tv[2], tdo[2], tdk, tdv;
     for (int i = 0; i < (TR::SPLIT ? 2 : 1); ++i) {
-        if (!make_tmap(&tq[i], q[i], false, TR::D, T, BH, TR::BQ) || !make_tmap(&tdo[i], dO[i], false, TR::D, T, BH, TR::BQ) ||
-            !make_tmap(&tk[i], k[i], false, TR::D, T, BH, TR::BKV) || !make_tmap(&tv[i], v[i], false, TR::D, T, BH, TR::BKV))
+        if (!make_tmap(&tq[i], q[i], false, TR::D, T, lq, BH, TR::BQ) || !make_tmap(&tdo[i], dO[i], false, TR::D, T, ldo, BH, TR::BQ) ||
+            !make_tmap(&tk[i], k[i], false, TR::D, T, lk, BH, TR::BKV) || !make_tmap(&tv[i], v[i], false, TR::D, T, lv, BH, TR::BKV))
             return IB200_ERR_CUDA;
     }
     if (!TR::SPLIT) { tq[1] = tq[0]; tk[1] = tk[0]; tv[1] = tv[0]; tdo[1] = tdo[0]; }
-    if (!make_tmap(&tdk, dk, TR::SPLIT, TR::D, T, BH, TR::BKV) || !make_tmap(&tdv, dv, TR::SPLIT, TR::D, T, BH, TR::BKV))
+    if (!make_tmap(&tdk, dk, TR::SPLIT, TR::D, T, ldk, BH, TR::BKV) || !make_tmap(&tdv, dv, TR::SPLIT, TR::D, T, ldv, BH, TR::BKV))
         return IB200_ERR_CUDA;
     // fp32 dQ accumulator, whole rows of D floats per box row, no swizzle (the staging tile is plain row-major)
     CUtensorMap tdq;
@@ -157,21 +173,27 @@ int launch_bwd(const void* const q[2], const void* const k[2], const void* const
     prm.status = status;
     prm.T = T;
     prm.BH = static_cast<int>(BH);
+    prm.H = lq.H;
     prm.causal = causal;
     prm.scale = scale;
     prm.scale_log2 = scale * 1.4426950408889634f;
     if (BH > 65535) return IB200_ERR_UNSUPPORTED;
     dim3 grid((T + TR::BKV - 1) / TR::BKV, static_cast<unsigned>(BH), 1);
-    if (g_ev[2]) cudaEventRecord(g_ev[2], stream);
+    record_timing_event(2, stream);
     attn_bwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq[0], tq[1], tk[0], tk[1], tv[0], tv[1], tdo[0], tdo[1], tdk, tdv, tdq, prm);
-    if (g_ev[3]) cudaEventRecord(g_ev[3], stream);
-    return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
+    const bool launched = cuda_ok(cudaGetLastError());
+    record_timing_event(3, stream);
+    return launched ? IB200_OK : IB200_ERR_CUDA;
 }
 
+struct BwdLayouts {
+    RowLayout q, k, v, o, dO, dq, dk, dv;
+};
+
 // delta pre-pass -> main kernel -> dQ finish.
-// Workspace: [header | dq accumulator | delta | (fp32 only) hi/lo bf16 copies of q, k, v, dO].
+// Workspace: [header | dq accumulator | -delta, -lse*log2e | (fp32 only) dense hi/lo bf16 copies of q, k, v, dO].
 int launch_bwd_all(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
-                   void* dq, void* dk, void* dv, long BH, int T, int D, float scale, int causal, bool f32,
+                   void* dq, void* dk, void* dv, const BwdLayouts& L, long BH, int T, int D, float scale, int causal, bool f32,
                    uint8_t* ws, cudaStream_t stream) {
     const long N = BH * T * D;
     int* status = reinterpret_cast<int*>(ws);
@@ -188,27 +210,43 @@ int launch_bwd_all(const void* q, const void* k, const void* v, const void* o, c
         const size_t slab = round_up(N * 2, 256);
         const void* part[8];
         const float* src[4] = {static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v), static_cast<const float*>(dO)};
+        const RowLayout* lsrc[4] = {&L.q, &L.k, &L.v, &L.dO};
         for (int i = 0; i < 4; ++i) {
             part[2 * i] = base + (2 * i) * slab;
             part[2 * i + 1] = base + (2 * i + 1) * slab;
-            rc = launch_split_bf16(src[i], const_cast<void*>(part[2 * i]), const_cast<void*>(part[2 * i + 1]), N, stream);
+            rc = launch_split_bf16(src[i], const_cast<void*>(part[2 * i]), const_cast<void*>(part[2 * i + 1]), *lsrc[i], BH, T, D, stream);
             if (rc) return rc;
         }
-        rc = launch_delta<64, true>(o, dO, lse, ndelta, nlse2, BH, T, T_pad, stream); if (rc) return rc;
-        rc = launch_bwd<BwdTraits<64, true>>(&part[0], &part[2], &part[4], &part[6], nlse2, ndelta, T_pad, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
+        const RowLayout dl = dense_layout(L.q.H, T, D);      // the hi/lo copies are dense
+        rc = launch_delta<64, true>(o, dO, lse, ndelta, nlse2, L.o, L.dO, BH, T, T_pad, stream); if (rc) return rc;
+        rc = launch_bwd<BwdTraits<64, true>>(&part[0], &part[2], &part[4], &part[6], dl, dl, dl, dl, L.dk, L.dv, nlse2, ndelta, T_pad,
+                                             dq_acc, dk, dv, status, BH, T, scale, causal, stream);
         if (rc) return rc;
-        return launch_dq_finish<true>(dq_acc, dq, scale, N, stream);
+        return launch_dq_finish<true>(dq_acc, dq, scale, L.dq, BH, T, D, stream);
     }
     const void* qq[2] = {q, q}; const void* kk[2] = {k, k}; const void* vv[2] = {v, v}; const void* dd[2] = {dO, dO};
     if (D == 64) {
-        rc = launch_delta<64, false>(o, dO, lse, ndelta, nlse2, BH, T, T_pad, stream); if (rc) return rc;
-        rc = launch_bwd<BwdTraits<64, false>>(qq, kk, vv, dd, nlse2, ndelta, T_pad, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
+        rc = launch_delta<64, false>(o, dO, lse, ndelta, nlse2, L.o, L.dO, BH, T, T_pad, stream); if (rc) return rc;
+        rc = launch_bwd<BwdTraits<64, false>>(qq, kk, vv, dd, L.q, L.k, L.v, L.dO, L.dk, L.dv, nlse2, ndelta, T_pad, dq_acc, dk, dv, status,
+                                              BH, T, scale, causal, stream);
     } else {
-        rc = launch_delta<128, false>(o, dO, lse, ndelta, nlse2, BH, T, T_pad, stream); if (rc) return rc;
-        rc = launch_bwd<BwdTraits<128, false>>(qq, kk, vv, dd, nlse2, ndelta, T_pad, dq_acc, dk, dv, status, BH, T, scale, causal, stream);
+        rc = launch_delta<128, false>(o, dO, lse, ndelta, nlse2, L.o, L.dO, BH, T, T_pad, stream); if (rc) return rc;
+        rc = launch_bwd<BwdTraits<128, false>>(qq, kk, vv, dd, L.q, L.k, L.v, L.dO, L.dk, L.dv, nlse2, ndelta, T_pad, dq_acc, dk, dv, status,
+                                               BH, T, scale, causal, stream);
     }
     if (rc) return rc;
-    return launch_dq_finish<false>(dq_acc, dq, scale, N, stream);
+    return launch_dq_finish<false>(dq_acc, dq, scale, L.dq, BH, T, D, stream);
+}
+
+// A caller-supplied layout (NULL = dense), checked: rows of D elements must start on 16-byte boundaries.
+int resolve_layout(const ib200_layout* in, int H, int T, int D, bool f32, RowLayout* out) {
+    if (!in) { *out = dense_layout(H, T, D); return IB200_OK; }
+    const long unit = f32 ? 4 : 8;      // elements per 16 bytes
+    if (in->stride_b <= 0 || in->stride_h <= 0 || in->stride_t <= 0) return IB200_ERR_INVALID_ARGUMENT;
+    if (in->stride_b % unit || in->stride_h % unit || in->stride_t % unit) return IB200_ERR_MISALIGNED;
+    if (in->stride_t < D || in->stride_h < D) return IB200_ERR_INVALID_ARGUMENT;
+    *out = RowLayout{static_cast<long>(in->stride_b), static_cast<long>(in->stride_h), static_cast<long>(in->stride_t), H};
+    return IB200_OK;
 }
 
 // Scratch for ib200_attn_bwd_static.  In host code this name is only a handle for the runtime; the
@@ -231,6 +269,81 @@ int static_scratch(void** out) {
     }
     *out = g_static_scratch_addr[dev];
     return IB200_OK;
+}
+
+int fwd_core(const void* q, const void* k, const void* v, void* o, float* lse, const ib200_layout* lq_, const ib200_layout* lk_,
+             const ib200_layout* lv_, const ib200_layout* lo_, int B, int H, int T, int D, float scale, int causal, int dtype,
+             int math_mode, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    if (!q || !k || !v || !o || !lse) return IB200_ERR_INVALID_ARGUMENT;
+    int rc = check_common(B, H, T, D, dtype, math_mode, causal);
+    if (rc != IB200_OK) return rc;
+    if (!(scale > 0.f) || !isfinite(scale)) return IB200_ERR_INVALID_ARGUMENT;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(lse)) return IB200_ERR_MISALIGNED;
+    const long BH = static_cast<long>(B) * H;
+    const long N = BH * T * D;
+    const bool f32 = dtype == IB200_DTYPE_F32;
+    RowLayout lq, lk, lv, lo;
+    if ((rc = resolve_layout(lq_, H, T, D, f32, &lq)) || (rc = resolve_layout(lk_, H, T, D, f32, &lk)) ||
+        (rc = resolve_layout(lv_, H, T, D, f32, &lv)) || (rc = resolve_layout(lo_, H, T, D, f32, &lo)))
+        return rc;
+    if (!workspace || !aligned16(workspace) || workspace_bytes < fwd_ws_bytes(N, f32)) return IB200_ERR_WORKSPACE;
+    rc = device_ok();
+    if (rc != IB200_OK) return rc;
+
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    int* status = reinterpret_cast<int*>(ws);
+    if (!cuda_ok(cudaMemsetAsync(ws, 0, kHeaderBytes, stream))) return IB200_ERR_CUDA;
+    if (f32) {
+        // fp32 operands are carried as dense (hi, lo) bf16 pairs
+        const size_t slab = round_up(N * 2, 256);
+        uint8_t* base = ws + kHeaderBytes;
+        void* part[6];
+        for (int i = 0; i < 6; ++i) part[i] = base + i * slab;
+        rc = launch_split_bf16(static_cast<const float*>(q), part[0], part[1], lq, BH, T, D, stream); if (rc) return rc;
+        rc = launch_split_bf16(static_cast<const float*>(k), part[2], part[3], lk, BH, T, D, stream); if (rc) return rc;
+        rc = launch_split_bf16(static_cast<const float*>(v), part[4], part[5], lv, BH, T, D, stream); if (rc) return rc;
+        const RowLayout dl = dense_layout(H, T, D);
+        return launch_fwd<FwdTraits<64, true>>(part[0], part[1], part[2], part[3], part[4], part[5], o, dl, dl, dl, lo, lse, status, BH, T,
+                                               scale, causal, stream);
+    }
+    if (D == 64) return launch_fwd<FwdTraits<64, false>>(q, q, k, k, v, v, o, lq, lk, lv, lo, lse, status, BH, T, scale, causal, stream);
+    return launch_fwd<FwdTraits<128, false>>(q, q, k, k, v, v, o, lq, lk, lv, lo, lse, status, BH, T, scale, causal, stream);
+}
+
+int bwd_core(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse, void* dq, void* dk, void* dv,
+             const ib200_layout* const lay[8], int B, int H, int T, int D, float scale, int causal, int dtype, int math_mode,
+             void* workspace, size_t workspace_bytes, bool use_static, cudaStream_t stream) {
+    if (!q || !k || !v || !o || !dO || !lse || !dq || !dk || !dv) return IB200_ERR_INVALID_ARGUMENT;
+    int rc = check_common(B, H, T, D, dtype, math_mode, causal);
+    if (rc != IB200_OK) return rc;
+    if (!(scale > 0.f) || !isfinite(scale)) return IB200_ERR_INVALID_ARGUMENT;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dO) || !aligned16(lse) ||
+        !aligned16(dq) || !aligned16(dk) || !aligned16(dv))
+        return IB200_ERR_MISALIGNED;
+    const long BH = static_cast<long>(B) * H;
+    const long N = BH * T * D;
+    const bool f32 = dtype == IB200_DTYPE_F32;
+    BwdLayouts L;
+    RowLayout* dst[8] = {&L.q, &L.k, &L.v, &L.o, &L.dO, &L.dq, &L.dk, &L.dv};
+    for (int i = 0; i < 8; ++i)
+        if ((rc = resolve_layout(lay[i], H, T, D, f32, dst[i]))) return rc;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    if (use_static) {
+        if (bwd_ws_bytes(N, BH, T, f32) > static_cast<size_t>(IB200_STATIC_SCRATCH_BYTES)) return IB200_ERR_TOO_LARGE;
+    } else if (!workspace || !aligned16(workspace) || workspace_bytes < bwd_ws_bytes(N, BH, T, f32)) {
+        return IB200_ERR_WORKSPACE;
+    }
+    rc = device_ok();
+    if (rc != IB200_OK) return rc;
+    if (use_static) {
+        void* scratch = nullptr;
+        rc = static_scratch(&scratch);
+        if (rc != IB200_OK) return rc;
+        ws = static_cast<uint8_t*>(scratch);
+    }
+    // launch_bwd_all clears the header and the dQ accumulator on `stream` and rewrites every other part of the
+    // scratch it reads, so stale contents of an earlier call (static scratch is shared) are never consumed
+    return launch_bwd_all(q, k, v, o, dO, lse, dq, dk, dv, L, BH, T, D, scale, causal, f32, ws, stream);
 }
 
 }  // namespace
@@ -278,83 +391,43 @@ int ib200_attn_workspace_bytes(int B, int H, int T, int D, int dtype, int pass, 
 
 int ib200_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H, int T, int D,
                    float scale, int causal, int dtype, int math_mode, void* workspace, size_t workspace_bytes,
-                   ib200_stream_t stream_) {
-    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-    if (!q || !k || !v || !o || !lse) return IB200_ERR_INVALID_ARGUMENT;
-    int rc = check_common(B, H, T, D, dtype, math_mode, causal);
-    if (rc != IB200_OK) return rc;
-    if (!(scale > 0.f) || !isfinite(scale)) return IB200_ERR_INVALID_ARGUMENT;
-    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(lse)) return IB200_ERR_MISALIGNED;
-    const long BH = static_cast<long>(B) * H;
-    const long N = BH * T * D;
-    const bool f32 = dtype == IB200_DTYPE_F32;
-    if (!workspace || !aligned16(workspace) || workspace_bytes < fwd_ws_bytes(N, f32)) return IB200_ERR_WORKSPACE;
-    rc = device_ok();
-    if (rc != IB200_OK) return rc;
+                   ib200_stream_t stream) {
+    return fwd_core(q, k, v, o, lse, nullptr, nullptr, nullptr, nullptr, B, H, T, D, scale, causal, dtype, math_mode, workspace,
+                    workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
 
-    uint8_t* ws = static_cast<uint8_t*>(workspace);
-    int* status = reinterpret_cast<int*>(ws);
-    if (!cuda_ok(cudaMemsetAsync(ws, 0, kHeaderBytes, stream))) return IB200_ERR_CUDA;
-    if (f32) {
-        // fp32 operands are carried as (hi, lo) bf16 pairs
-        const size_t slab = round_up(N * 2, 256);
-        uint8_t* base = ws + kHeaderBytes;
-        void* part[6];
-        for (int i = 0; i < 6; ++i) part[i] = base + i * slab;
-        rc = launch_split_bf16(static_cast<const float*>(q), part[0], part[1], N, stream); if (rc) return rc;
-        rc = launch_split_bf16(static_cast<const float*>(k), part[2], part[3], N, stream); if (rc) return rc;
-        rc = launch_split_bf16(static_cast<const float*>(v), part[4], part[5], N, stream); if (rc) return rc;
-        return launch_fwd<FwdTraits<64, true>>(part[0], part[1], part[2], part[3], part[4], part[5], o, lse, status, BH, T, scale, causal, stream);
-    }
-    if (D == 64) return launch_fwd<FwdTraits<64, false>>(q, q, k, k, v, v, o, lse, status, BH, T, scale, causal, stream);
-    return launch_fwd<FwdTraits<128, false>>(q, q, k, k, v, v, o, lse, status, BH, T, scale, causal, stream);
+int ib200_attn_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse, const ib200_layout* lq,
+                           const ib200_layout* lk, const ib200_layout* lv, const ib200_layout* lo, int B, int H, int T, int D,
+                           float scale, int causal, int dtype, int math_mode, void* workspace, size_t workspace_bytes,
+                           ib200_stream_t stream) {
+    return fwd_core(q, k, v, o, lse, lq, lk, lv, lo, B, H, T, D, scale, causal, dtype, math_mode, workspace, workspace_bytes,
+                    reinterpret_cast<cudaStream_t>(stream));
 }
 
 int ib200_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
                    void* dq, void* dk, void* dv, int B, int H, int T, int D, float scale, int causal, int dtype,
-                   int math_mode, void* workspace, size_t workspace_bytes, ib200_stream_t stream_) {
-    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-    if (!q || !k || !v || !o || !dO || !lse || !dq || !dk || !dv) return IB200_ERR_INVALID_ARGUMENT;
-    int rc = check_common(B, H, T, D, dtype, math_mode, causal);
-    if (rc != IB200_OK) return rc;
-    if (!(scale > 0.f) || !isfinite(scale)) return IB200_ERR_INVALID_ARGUMENT;
-    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dO) || !aligned16(lse) ||
-        !aligned16(dq) || !aligned16(dk) || !aligned16(dv))
-        return IB200_ERR_MISALIGNED;
-    const long BH = static_cast<long>(B) * H;
-    const long N = BH * T * D;
-    const bool f32 = dtype == IB200_DTYPE_F32;
-    if (!workspace || !aligned16(workspace) || workspace_bytes < bwd_ws_bytes(N, BH, T, f32)) return IB200_ERR_WORKSPACE;
-    rc = device_ok();
-    if (rc != IB200_OK) return rc;
-    return launch_bwd_all(q, k, v, o, dO, lse, dq, dk, dv, BH, T, D, scale, causal, f32,
-                          static_cast<uint8_t*>(workspace), stream);
+                   int math_mode, void* workspace, size_t workspace_bytes, ib200_stream_t stream) {
+    const ib200_layout* lay[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    return bwd_core(q, k, v, o, dO, lse, dq, dk, dv, lay, B, H, T, D, scale, causal, dtype, math_mode, workspace, workspace_bytes,
+                    false, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ib200_attn_bwd_strided(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
+                           void* dq, void* dk, void* dv, const ib200_layout* lq, const ib200_layout* lk, const ib200_layout* lv,
+                           const ib200_layout* lo, const ib200_layout* ldo, const ib200_layout* ldq, const ib200_layout* ldk,
+                           const ib200_layout* ldv, int B, int H, int T, int D, float scale, int causal, int dtype, int math_mode,
+                           void* workspace, size_t workspace_bytes, ib200_stream_t stream) {
+    const ib200_layout* lay[8] = {lq, lk, lv, lo, ldo, ldq, ldk, ldv};
+    return bwd_core(q, k, v, o, dO, lse, dq, dk, dv, lay, B, H, T, D, scale, causal, dtype, math_mode, workspace, workspace_bytes,
+                    false, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int ib200_attn_bwd_static(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
                           void* dq, void* dk, void* dv, int B, int H, int T, int D, float scale, int causal, int dtype,
-                          int math_mode, ib200_stream_t stream_) {
-    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-    if (!q || !k || !v || !o || !dO || !lse || !dq || !dk || !dv) return IB200_ERR_INVALID_ARGUMENT;
-    int rc = check_common(B, H, T, D, dtype, math_mode, causal);
-    if (rc != IB200_OK) return rc;
-    if (!(scale > 0.f) || !isfinite(scale)) return IB200_ERR_INVALID_ARGUMENT;
-    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dO) || !aligned16(lse) ||
-        !aligned16(dq) || !aligned16(dk) || !aligned16(dv))
-        return IB200_ERR_MISALIGNED;
-    const long BH = static_cast<long>(B) * H;
-    const long N = BH * T * D;
-    const bool f32 = dtype == IB200_DTYPE_F32;
-    if (bwd_ws_bytes(N, BH, T, f32) > static_cast<size_t>(IB200_STATIC_SCRATCH_BYTES)) return IB200_ERR_TOO_LARGE;
-    rc = device_ok();
-    if (rc != IB200_OK) return rc;
-    void* scratch = nullptr;
-    rc = static_scratch(&scratch);
-    if (rc != IB200_OK) return rc;
-    // launch_bwd_all clears the header and the dQ accumulator on `stream` and rewrites every other
-    // part of the scratch it reads, so stale contents of an earlier call are never consumed
-    return launch_bwd_all(q, k, v, o, dO, lse, dq, dk, dv, BH, T, D, scale, causal, f32,
-                          static_cast<uint8_t*>(scratch), stream);
+                          int math_mode, ib200_stream_t stream) {
+    const ib200_layout* lay[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    return bwd_core(q, k, v, o, dO, lse, dq, dk, dv, lay, B, H, T, D, scale, causal, dtype, math_mode, nullptr, 0, true,
+                    reinterpret_cast<cudaStream_t>(stream));
 }
 
 int ib200_attn_check(const void* workspace, ib200_stream_t stream_, int* device_code) {

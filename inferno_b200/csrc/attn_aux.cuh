@@ -15,13 +15,33 @@
 
 namespace ib200 {
 
+// Where the rows of a [B, H, T, D] operand live: element strides of the batch, head and token axes
+// (the D elements of a row are contiguous).  Dense row-major is {H*T*D, T*D, D}; a q/k/v slice of a packed
+// [B, T, 3, H, D] projection is {T*3*H*D, D, 3*H*D}.
+struct RowLayout {
+    long sb, sh, st;
+    int H;
+    __host__ __device__ long row(long head, int t) const { return (head / H) * sb + (head % H) * sh + static_cast<long>(t) * st; }
+};
+inline RowLayout dense_layout(int H, int T, int D) { return RowLayout{static_cast<long>(H) * T * D, static_cast<long>(T) * D, D, H}; }
+
 constexpr int kAuxThreads = 256;
 constexpr int kAuxBlocks = 148 * 8;
 
 // hi = bf16(x), lo = bf16(x - hi): 8 elements per thread, two 16-byte loads, two 16-byte stores.
-__global__ void __launch_bounds__(kAuxThreads) split_bf16_kernel(const float4* __restrict__ in, uint4* __restrict__ hi, uint4* __restrict__ lo, long n8) {
+// Reads rows through `lin` (any layout) and writes hi / lo dense, so the main kernels always see dense
+// operand copies in fp32-I/O mode.
+__global__ void __launch_bounds__(kAuxThreads) split_bf16_kernel(const float* __restrict__ in, uint4* __restrict__ hi, uint4* __restrict__ lo,
+                                                                 RowLayout lin, long heads, int T, int D) {
+    const int cpr = D / 8;                                   // 8-element chunks per row
+    const long n8 = heads * T * cpr;
     for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
-        const float4 a = in[2 * i], b = in[2 * i + 1];
+        const long rowi = i / cpr;
+        const int c8 = static_cast<int>(i - rowi * cpr);
+        const long head = rowi / T;
+        const int t = static_cast<int>(rowi - head * T);
+        const float4* src = reinterpret_cast<const float4*>(in + lin.row(head, t) + c8 * 8);
+        const float4 a = src[0], b = src[1];
         const float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
         uint32_t h[4], l[4];
 #pragma unroll
@@ -37,11 +57,11 @@ __global__ void __launch_bounds__(kAuxThreads) split_bf16_kernel(const float4* _
     }
 }
 
-inline int launch_split_bf16(const float* in, void* hi, void* lo, long n, cudaStream_t stream) {
-    const long n8 = n / 8;
+inline int launch_split_bf16(const float* in, void* hi, void* lo, const RowLayout& lin, long heads, int T, int D, cudaStream_t stream) {
+    const long n8 = heads * T * D / 8;
     long blocks = n8 / kAuxThreads + 1;
     if (blocks > kAuxBlocks) blocks = kAuxBlocks;
-    split_bf16_kernel<<<static_cast<int>(blocks), kAuxThreads, 0, stream>>>(reinterpret_cast<const float4*>(in), reinterpret_cast<uint4*>(hi), reinterpret_cast<uint4*>(lo), n8);
+    split_bf16_kernel<<<static_cast<int>(blocks), kAuxThreads, 0, stream>>>(in, reinterpret_cast<uint4*>(hi), reinterpret_cast<uint4*>(lo), lin, heads, T, D);
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 
@@ -53,7 +73,8 @@ inline int launch_split_bf16(const float* in, void* hi, void* lo, long n, cudaSt
 // Padding rows (t >= T) are written as 0.
 template <int D, bool F32>
 __global__ void __launch_bounds__(kAuxThreads) delta_kernel(const void* __restrict__ o_, const void* __restrict__ do_, const float* __restrict__ lse,
-                                                            float* __restrict__ ndelta, float* __restrict__ nlse2, long heads, int T, int T_pad) {
+                                                            float* __restrict__ ndelta, float* __restrict__ nlse2, RowLayout lo, RowLayout ldo,
+                                                            long heads, int T, int T_pad) {
     constexpr int EPT = F32 ? 4 : 8;              // elements per 16-byte load
     constexpr int TPR = D / EPT;                  // threads per row (8 or 16)
     constexpr int RPB = kAuxThreads / TPR;        // rows per block per step
@@ -68,12 +89,12 @@ __global__ void __launch_bounds__(kAuxThreads) delta_kernel(const void* __restri
         float acc = 0.f;
         if (live) {
             if constexpr (F32) {
-                const float4 a = reinterpret_cast<const float4*>(o_)[row * TPR + sub];
-                const float4 b = reinterpret_cast<const float4*>(do_)[row * TPR + sub];
+                const float4 a = reinterpret_cast<const float4*>(static_cast<const float*>(o_) + lo.row(head, t))[sub];
+                const float4 b = reinterpret_cast<const float4*>(static_cast<const float*>(do_) + ldo.row(head, t))[sub];
                 acc = a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
             } else {
-                const uint4 a = reinterpret_cast<const uint4*>(o_)[row * TPR + sub];
-                const uint4 b = reinterpret_cast<const uint4*>(do_)[row * TPR + sub];
+                const uint4 a = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(o_) + lo.row(head, t))[sub];
+                const uint4 b = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(do_) + ldo.row(head, t))[sub];
                 const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
                 const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
 #pragma unroll
@@ -94,44 +115,53 @@ __global__ void __launch_bounds__(kAuxThreads) delta_kernel(const void* __restri
 }
 
 template <int D, bool F32>
-inline int launch_delta(const void* o, const void* dO, const float* lse, float* ndelta, float* nlse2, long heads, int T, int T_pad,
-                        cudaStream_t stream) {
+inline int launch_delta(const void* o, const void* dO, const float* lse, float* ndelta, float* nlse2, const RowLayout& lo,
+                        const RowLayout& ldo, long heads, int T, int T_pad, cudaStream_t stream) {
     constexpr int RPB = kAuxThreads / (D / (F32 ? 4 : 8));
     // every thread of a block takes part in the shuffles: the row loop bound is uniform per TPR group
     long blocks = (heads * T_pad + RPB - 1) / RPB;
     if (blocks > kAuxBlocks) blocks = kAuxBlocks;
-    delta_kernel<D, F32><<<static_cast<int>(blocks), kAuxThreads, 0, stream>>>(o, dO, lse, ndelta, nlse2, heads, T, T_pad);
+    delta_kernel<D, F32><<<static_cast<int>(blocks), kAuxThreads, 0, stream>>>(o, dO, lse, ndelta, nlse2, lo, ldo, heads, T, T_pad);
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 
-// out[i] = scale * acc[i], 8 elements per thread.
+// out[row, :] = scale * acc[row, :], 8 elements per thread; acc is dense [heads, T, D], out follows `lout`.
 template <bool F32>
-__global__ void __launch_bounds__(kAuxThreads) dq_finish_kernel(const float4* __restrict__ acc, void* __restrict__ out, float scale, long n8) {
+__global__ void __launch_bounds__(kAuxThreads) dq_finish_kernel(const float4* __restrict__ acc, void* __restrict__ out, float scale,
+                                                                RowLayout lout, long heads, int T, int D) {
+    const int cpr = D / 8;
+    const long n8 = heads * T * cpr;
     for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
+        const long rowi = i / cpr;
+        const int c8 = static_cast<int>(i - rowi * cpr);
+        const long head = rowi / T;
+        const int t = static_cast<int>(rowi - head * T);
+        const long dst = lout.row(head, t) + c8 * 8;
         float4 a = acc[2 * i], b = acc[2 * i + 1];
         a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
         b.x *= scale; b.y *= scale; b.z *= scale; b.w *= scale;
         if constexpr (F32) {
-            reinterpret_cast<float4*>(out)[2 * i] = a;
-            reinterpret_cast<float4*>(out)[2 * i + 1] = b;
+            float4* o4 = reinterpret_cast<float4*>(static_cast<float*>(out) + dst);
+            o4[0] = a;
+            o4[1] = b;
         } else {
             uint4 v;
-            __nv_bfloat162 t;
-            t = __floats2bfloat162_rn(a.x, a.y); v.x = *reinterpret_cast<uint32_t*>(&t);
-            t = __floats2bfloat162_rn(a.z, a.w); v.y = *reinterpret_cast<uint32_t*>(&t);
-            t = __floats2bfloat162_rn(b.x, b.y); v.z = *reinterpret_cast<uint32_t*>(&t);
-            t = __floats2bfloat162_rn(b.z, b.w); v.w = *reinterpret_cast<uint32_t*>(&t);
-            reinterpret_cast<uint4*>(out)[i] = v;
+            __nv_bfloat162 t2;
+            t2 = __floats2bfloat162_rn(a.x, a.y); v.x = *reinterpret_cast<uint32_t*>(&t2);
+            t2 = __floats2bfloat162_rn(a.z, a.w); v.y = *reinterpret_cast<uint32_t*>(&t2);
+            t2 = __floats2bfloat162_rn(b.x, b.y); v.z = *reinterpret_cast<uint32_t*>(&t2);
+            t2 = __floats2bfloat162_rn(b.z, b.w); v.w = *reinterpret_cast<uint32_t*>(&t2);
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out) + dst) = v;
         }
     }
 }
 
 template <bool F32>
-inline int launch_dq_finish(const float* acc, void* out, float scale, long n, cudaStream_t stream) {
-    const long n8 = n / 8;
+inline int launch_dq_finish(const float* acc, void* out, float scale, const RowLayout& lout, long heads, int T, int D, cudaStream_t stream) {
+    const long n8 = heads * T * D / 8;
     long blocks = n8 / kAuxThreads + 1;
     if (blocks > kAuxBlocks) blocks = kAuxBlocks;
-    dq_finish_kernel<F32><<<static_cast<int>(blocks), kAuxThreads, 0, stream>>>(reinterpret_cast<const float4*>(acc), out, scale, n8);
+    dq_finish_kernel<F32><<<static_cast<int>(blocks), kAuxThreads, 0, stream>>>(reinterpret_cast<const float4*>(acc), out, scale, lout, heads, T, D);
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 

@@ -87,7 +87,7 @@ struct BwdParams {
     const float* ndelta;   // [BH, T_pad]  -rowsum(dO * O), 0 in the padding
     int T_pad;             // T rounded up to a multiple of 64
     int* status;
-    int T, BH, causal;
+    int T, BH, H, causal;  // H: heads per batch entry (operand tensor maps are 4-D: column, token, head, batch)
     float scale, scale_log2;
 };
 
@@ -187,6 +187,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int T = prm.T;
     const int bh = blockIdx.y;
+    const int hd = bh % prm.H, bt = bh / prm.H;                 // head and batch coordinates
     const int n = blockIdx.x;                                   // key tile; tile 0 walks the most query blocks and starts first
     const int nqb = (T + BQ - 1) / BQ;
     const int m0 = prm.causal ? (n * BKV) / BQ : 0;             // first query block at or below the diagonal
@@ -226,8 +227,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mbar_arrive_expect_tx(kv_full, 2 * TR::KV_TILE);
             for (int p = 0; p < TR::NP; ++p) {
                 const bool lo = TR::SPLIT && p;
-                tma_load_3d(sK + p * TR::KV_PANEL, lo ? &tm_k_lo : &tm_k, kv_full, TR::SPLIT ? 0 : p * 64, n * BKV, bh);
-                tma_load_3d(sV + p * TR::KV_PANEL, lo ? &tm_v_lo : &tm_v, kv_full, TR::SPLIT ? 0 : p * 64, n * BKV, bh);
+                tma_load_4d(sK + p * TR::KV_PANEL, lo ? &tm_k_lo : &tm_k, kv_full, TR::SPLIT ? 0 : p * 64, n * BKV, hd, bt);
+                tma_load_4d(sV + p * TR::KV_PANEL, lo ? &tm_v_lo : &tm_v, kv_full, TR::SPLIT ? 0 : p * 64, n * BKV, hd, bt);
             }
         }
         if (lane == 0) {
@@ -238,8 +239,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 mbar_arrive_expect_tx(&qdo_full[s], 2 * TR::Q_TILE + 2 * BQ * 4);
                 for (int p = 0; p < TR::NP; ++p) {
                     const bool lo = TR::SPLIT && p;
-                    tma_load_3d(sQ + s * TR::Q_TILE + p * TR::Q_PANEL, lo ? &tm_q_lo : &tm_q, &qdo_full[s], TR::SPLIT ? 0 : p * 64, m * BQ, bh);
-                    tma_load_3d(sDO + s * TR::Q_TILE + p * TR::Q_PANEL, lo ? &tm_do_lo : &tm_do, &qdo_full[s], TR::SPLIT ? 0 : p * 64, m * BQ, bh);
+                    tma_load_4d(sQ + s * TR::Q_TILE + p * TR::Q_PANEL, lo ? &tm_q_lo : &tm_q, &qdo_full[s], TR::SPLIT ? 0 : p * 64, m * BQ, hd, bt);
+                    tma_load_4d(sDO + s * TR::Q_TILE + p * TR::Q_PANEL, lo ? &tm_do_lo : &tm_do, &qdo_full[s], TR::SPLIT ? 0 : p * 64, m * BQ, hd, bt);
                 }
                 // the block's 64 values of -lse*log2e and of -delta (padded rows, so always aligned and in range)
                 const size_t voff = static_cast<size_t>(bh) * prm.T_pad + static_cast<size_t>(m) * BQ;
@@ -412,7 +413,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             asm volatile("bar.sync %0, 128;" ::"r"(1 + h) : "memory");
             if ((tid & 127) == 0) {
                 for (int p = 0; p < TR::OUT_PANELS; ++p)
-                    tma_store_3d(h ? &tm_dk : &tm_dv, stage + p * TR::KV_PANEL, p * TR::OUT_PANEL_ELEMS, n * BKV, bh);
+                    tma_store_4d(h ? &tm_dk : &tm_dv, stage + p * TR::KV_PANEL, p * TR::OUT_PANEL_ELEMS, n * BKV, hd, bt);
                 tma_store_commit();
                 tma_store_wait_all();
             }

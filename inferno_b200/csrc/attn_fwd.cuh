@@ -59,7 +59,7 @@ struct FwdTraits {
 struct FwdParams {
     float* lse;            // [BH, T] natural-log units, scale included
     int* status;           // device status word (0 = ok)
-    int T, BH;
+    int T, BH, H;          // H: heads per batch entry (the tensor maps are 4-D: column, token, head, batch)
     int causal;
     float scale_log2;      // scale * log2(e)
 };
@@ -134,6 +134,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int T = prm.T;
     const int bh = blockIdx.y;
+    const int hd = bh % prm.H, bt = bh / prm.H;            // head and batch coordinates
     const int pair = (gridDim.x - 1) - blockIdx.x;          // heaviest (longest walk) first
     const int m_tile[2] = {2 * pair, 2 * pair + 1};
     const int n_kv_total = (T + BN - 1) / BN;
@@ -172,18 +173,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mbar_arrive_expect_tx(q_full, q_tiles * TR::TILE_BYTES);
             for (int i = 0; i < q_tiles; ++i)
                 for (int p = 0; p < TR::NP; ++p)
-                    tma_load_3d(sQ + i * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_q_lo : &tm_q, q_full, TR::SPLIT ? 0 : p * 64, m_tile[i] * BM, bh);
+                    tma_load_4d(sQ + i * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_q_lo : &tm_q, q_full, TR::SPLIT ? 0 : p * 64, m_tile[i] * BM, hd, bt);
             for (int j = 0; j < n_iter; ++j) {
                 const int s = j % KS;
                 const uint32_t ph = (j / KS) & 1;
                 mbar_wait(&k_empty[s], ph ^ 1, ab, 10);
                 mbar_arrive_expect_tx(&k_full[s], TR::TILE_BYTES);
                 for (int p = 0; p < TR::NP; ++p)
-                    tma_load_3d(sK + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_k_lo : &tm_k, &k_full[s], TR::SPLIT ? 0 : p * 64, j * BN, bh);
+                    tma_load_4d(sK + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_k_lo : &tm_k, &k_full[s], TR::SPLIT ? 0 : p * 64, j * BN, hd, bt);
                 mbar_wait(&v_empty[s], ph ^ 1, ab, 11);
                 mbar_arrive_expect_tx(&v_full[s], TR::TILE_BYTES);
                 for (int p = 0; p < TR::NP; ++p)
-                    tma_load_3d(sV + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_v_lo : &tm_v, &v_full[s], TR::SPLIT ? 0 : p * 64, j * BN, bh);
+                    tma_load_4d(sV + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_v_lo : &tm_v, &v_full[s], TR::SPLIT ? 0 : p * 64, j * BN, hd, bt);
             }
         }
     } else if (warp == 8) {
@@ -364,7 +365,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             asm volatile("bar.sync %0, 128;" ::"r"(1 + i) : "memory");
             if (t == 0) {
                 for (int p = 0; p < TR::OUT_PANELS; ++p)
-                    tma_store_3d(&tm_o, stage + p * TR::PANEL_BYTES, p * TR::OUT_PANEL_ELEMS, m_tile[i] * BM, bh);
+                    tma_store_4d(&tm_o, stage + p * TR::PANEL_BYTES, p * TR::OUT_PANEL_ELEMS, m_tile[i] * BM, hd, bt);
                 tma_store_commit();
                 tma_store_wait_all();
             }

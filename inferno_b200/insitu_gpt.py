@@ -42,6 +42,9 @@ class Block(nn.Module):
 
     def attention(self, x: torch.Tensor) -> torch.Tensor:
         B, T, C = x.shape
+        if self.attn_impl == "ib200_packed":
+            # the kernels read q, k, v in place inside the projection output and write [B,T,H,D]: no layout copies
+            return self.wout(A.causal_attention_packed(self.wqkv(x), self.H))
         q, k, v = self.wqkv(x).split(C, dim=2)
         q, k, v = (t.reshape(B, T, self.H, C // self.H).transpose(1, 2).contiguous() for t in (q, k, v))   # [B,H,T,D]
         if self.attn_impl == "ib200":
@@ -84,10 +87,10 @@ def train_step(model, opt, idx, tgt):
     return loss
 
 
-def run(layers=12, C=768, H=12, vocab=8192, T=1024, B=16, steps=5, warmup=3, seed=3):
+def run(layers=12, C=768, H=12, vocab=8192, T=1024, B=16, steps=5, warmup=3, seed=3, attn_impl="ib200"):
     dev = torch.device("cuda", torch.cuda.current_device())
     torch.manual_seed(seed)
-    model = GPT(vocab, T, C, H, layers).to(dev).to(torch.bfloat16)
+    model = GPT(vocab, T, C, H, layers, attn_impl).to(dev).to(torch.bfloat16)
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
     g = torch.Generator(device=dev).manual_seed(seed)
     idx = torch.randint(0, vocab, (B, T), device=dev, generator=g)
@@ -108,12 +111,18 @@ def run(layers=12, C=768, H=12, vocab=8192, T=1024, B=16, steps=5, warmup=3, see
         def fwd_hook(*a, **kw):
             i = calls["f"]; calls["f"] += 1
             A.set_timing_events(evs[i][0], evs[i][1], None, None)
-            return orig_f(*a, **kw)
+            try:
+                return orig_f(*a, **kw)
+            finally:
+                A.set_timing_events()          # the hook is per host thread: switch it off where it was switched on
 
         def bwd_hook(*a, **kw):
             i = layers - 1 - calls["b"]; calls["b"] += 1
             A.set_timing_events(None, None, evs[i][2], evs[i][3])
-            return orig_b(*a, **kw)
+            try:
+                return orig_b(*a, **kw)       # runs on autograd's worker thread
+            finally:
+                A.set_timing_events()
 
         A.attention_forward, A.attention_backward = fwd_hook, bwd_hook
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -132,7 +141,7 @@ def run(layers=12, C=768, H=12, vocab=8192, T=1024, B=16, steps=5, warmup=3, see
     D = C // H
     unit = B * H * float(T) ** 2 * D * layers
     f, b, s = (sorted(x)[len(x) // 2] for x in (fwd_ms, bwd_ms, step_ms))
-    return dict(config=dict(layers=layers, d_model=C, heads=H, d_head=D, vocab=vocab, T=T, B=B, dtype="bf16"),
+    return dict(config=dict(layers=layers, d_model=C, heads=H, d_head=D, vocab=vocab, T=T, B=B, dtype="bf16", attn_impl=attn_impl),
                 loss=float(loss.detach()), step_ms=s, attn_fwd_ms=f, attn_bwd_main_ms=b,
                 attn_fwd_tflops=2 * unit / (f * 1e-3) / 1e12, attn_bwd_tflops=5 * unit / (b * 1e-3) / 1e12,
                 attn_share_of_step=(f + b) / s)
@@ -144,5 +153,7 @@ if __name__ == "__main__":
     ap.add_argument("--heads", type=int, default=12); ap.add_argument("--vocab", type=int, default=8192)
     ap.add_argument("--T", type=int, default=1024); ap.add_argument("--B", type=int, default=16)
     ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--attn", default="ib200", choices=["ib200", "ib200_packed"],
+                    help="ib200: dense [B,H,T,D] operands (the reference's layout copies stay); ib200_packed: operands read in place")
     a = ap.parse_args()
-    print(json.dumps(run(a.layers, a.d_model, a.heads, a.vocab, a.T, a.B, a.steps)))
+    print(json.dumps(run(a.layers, a.d_model, a.heads, a.vocab, a.T, a.B, a.steps, attn_impl=a.attn)))
