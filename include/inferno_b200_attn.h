@@ -100,6 +100,24 @@ int ib200_attn_bwd_strided(const void* q, const void* k, const void* v, const vo
                            int B, int H, int T, int D, float scale, int causal, int dtype, int math_mode,
                            void* workspace, size_t workspace_bytes, ib200_stream_t stream);
 
+/* The projections either side of attention.  C[M,N] = A[M,K] B[K,N] (+ bias[N]), bf16 operands and output, fp32
+ * accumulation on the tensor cores, fp32 bias.  a_transposed = 0: A stored [M rows, K contiguous]; 1: stored
+ * [K rows, M contiguous].  b_transposed = 0: B stored [K rows, N contiguous]; 1: stored [N rows, K contiguous].
+ * M, N, K multiples of 8; bases 16-byte aligned.  Replaces cublas_mm_row_major + the broadcast add of the reference's
+ * Linear::forward (src/inferno/modules/linear.cpp:99-106, src/inferno/cuda/cudamatmul.cu:1058-1112,
+ * src/inferno/cuda/cudaadd.cu:20-142); a transposed operand costs a descriptor, not the copy the reference makes
+ * (src/inferno/gradfn/mmbackward.cpp:77-80). */
+int ib200_gemm_bf16(const void* a, const void* b, void* c, const float* bias, int M, int N, int K,
+                    int a_transposed, int b_transposed, ib200_stream_t stream);
+
+/* y[M,N] = x[M,K] w[K,N] + bias[N]  (Linear::forward, weight stored [in, out] as in the reference). */
+int ib200_linear_fwd(const void* x, const void* w, const float* bias, void* y, int M, int K, int N, ib200_stream_t stream);
+
+/* dx[M,K] = dy w^T, dw[K,N] = x^T dy, db[N] = column sums of dy (fp32); any of dx / dw / db may be NULL.
+ * Replaces MMBackward (src/inferno/gradfn/mmbackward.cpp:36-98) and the bias gradient's sum_to_shape for a Linear. */
+int ib200_linear_bwd(const void* x, const void* w, const void* dy, void* dx, void* dw, float* db,
+                     int M, int K, int N, ib200_stream_t stream);
+
 /* Capacity in bytes of the scratch buffer that is compiled into the library for
  * ib200_attn_bwd_static (one copy lives in the memory of every GPU that loads the library,
  * from load until the process exits). */

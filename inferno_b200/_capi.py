@@ -19,7 +19,7 @@ PASS_FWD, PASS_BWD = 0, 1
 
 EXPORTS = (
     "ib200_attn_workspace_bytes", "ib200_attn_fwd", "ib200_attn_bwd", "ib200_attn_check",
-    "ib200_status_string", "ib200_last_cuda_error", "ib200_version", "ib200_attn_set_timing_events", "ib200_attn_bwd_static", "ib200_attn_fwd_strided", "ib200_attn_bwd_strided",
+    "ib200_status_string", "ib200_last_cuda_error", "ib200_version", "ib200_attn_set_timing_events", "ib200_attn_bwd_static", "ib200_attn_fwd_strided", "ib200_attn_bwd_strided", "ib200_gemm_bf16", "ib200_linear_fwd", "ib200_linear_bwd",
 )
 
 
@@ -61,6 +61,12 @@ def lib() -> ctypes.CDLL:
         L.ib200_attn_bwd_strided.restype = i
         L.ib200_attn_bwd_static.argtypes = [vp] * 9 + [i, i, i, i, f, i, i, i, vp]
         L.ib200_attn_bwd_static.restype = i
+        L.ib200_gemm_bf16.argtypes = [vp, vp, vp, vp, i, i, i, i, i, vp]
+        L.ib200_gemm_bf16.restype = i
+        L.ib200_linear_fwd.argtypes = [vp, vp, vp, vp, i, i, i, vp]
+        L.ib200_linear_fwd.restype = i
+        L.ib200_linear_bwd.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, vp]
+        L.ib200_linear_bwd.restype = i
         L.ib200_attn_check.argtypes = [vp, vp, ctypes.POINTER(i)]
         L.ib200_attn_check.restype = i
         L.ib200_attn_set_timing_events.argtypes = [vp, vp, vp, vp]

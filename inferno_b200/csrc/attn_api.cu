@@ -9,6 +9,7 @@
 #include "attn_aux.cuh"
 #include "attn_bwd.cuh"
 #include "attn_fwd.cuh"
+#include "linear_gemm.cuh"
 
 namespace {
 
@@ -64,6 +65,18 @@ bool make_tmap(CUtensorMap* m, const void* base, bool f32, int D, int T, const R
                      const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
+}
+
+// Tensor map over a row-major bf16 matrix [rows, cols]; box = [box_rows x 64 columns], 128B swizzle.
+bool make_tmap_2d(CUtensorMap* m, const void* base, long rows, long cols, int box_rows) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return false;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), 1};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * 2, static_cast<cuuint64_t>(rows) * static_cast<cuuint64_t>(cols) * 2};
+    cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -271,6 +284,43 @@ int static_scratch(void** out) {
     return IB200_OK;
 }
 
+template <bool A_MN, bool B_MN>
+int launch_gemm(const void* a, const void* b, void* c, const float* bias, int M, int N, int K, cudaStream_t stream) {
+    using TR = GemmTraits;
+    // a runtime call first: it makes the primary context current on this host thread (a framework's worker
+    // thread may never have touched CUDA), which the driver's tensor-map encoder needs
+    if (!cuda_ok(cudaFuncSetAttribute(gemm_bf16_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::SMEM_BYTES)))
+        return IB200_ERR_CUDA;
+    CUtensorMap ta, tb, tc;
+    // A: [M,K] (box 128 rows) or stored [K,M] (box 64 k-rows); B: stored [K,N] (box 64 k-rows) or [N,K] (box 256 rows)
+    const bool ok = (A_MN ? make_tmap_2d(&ta, a, K, M, 64) : make_tmap_2d(&ta, a, M, K, 128)) &&
+                    (B_MN ? make_tmap_2d(&tb, b, K, N, 64) : make_tmap_2d(&tb, b, N, K, 256)) && make_tmap_2d(&tc, c, M, N, 128);
+    if (!ok) return IB200_ERR_CUDA;
+    int dev = 0, sms = 148;
+    if (cuda_ok(cudaGetDevice(&dev))) (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long tiles = static_cast<long>((M + TR::BM - 1) / TR::BM) * ((N + TR::BN - 1) / TR::BN);
+    GemmParams prm;
+    prm.bias = bias;
+    prm.M = M; prm.N = N; prm.K = K;
+    prm.status = nullptr;
+    const int grid = static_cast<int>(tiles < sms ? tiles : sms);       // persistent: one CTA per SM
+    gemm_bf16_kernel<A_MN, B_MN><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(ta, tb, tc, prm);
+    return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
+}
+
+int gemm_dispatch(const void* a, const void* b, void* c, const float* bias, int M, int N, int K, int a_t, int b_t, cudaStream_t stream) {
+    if (!a || !b || !c) return IB200_ERR_INVALID_ARGUMENT;
+    if (M <= 0 || N <= 0 || K <= 0 || (a_t != 0 && a_t != 1) || (b_t != 0 && b_t != 1)) return IB200_ERR_INVALID_ARGUMENT;
+    if (M % 8 || N % 8 || K % 8) return IB200_ERR_UNSUPPORTED;
+    if (!aligned16(a) || !aligned16(b) || !aligned16(c) || (bias && !aligned16(bias))) return IB200_ERR_MISALIGNED;
+    int rc = device_ok();
+    if (rc != IB200_OK) return rc;
+    if (!a_t && !b_t) return launch_gemm<false, true>(a, b, c, bias, M, N, K, stream);
+    if (!a_t && b_t) return launch_gemm<false, false>(a, b, c, bias, M, N, K, stream);
+    if (a_t && !b_t) return launch_gemm<true, true>(a, b, c, bias, M, N, K, stream);
+    return launch_gemm<true, false>(a, b, c, bias, M, N, K, stream);
+}
+
 int fwd_core(const void* q, const void* k, const void* v, void* o, float* lse, const ib200_layout* lq_, const ib200_layout* lk_,
              const ib200_layout* lv_, const ib200_layout* lo_, int B, int H, int T, int D, float scale, int causal, int dtype,
              int math_mode, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
@@ -428,6 +478,32 @@ int ib200_attn_bwd_static(const void* q, const void* k, const void* v, const voi
     const ib200_layout* lay[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     return bwd_core(q, k, v, o, dO, lse, dq, dk, dv, lay, B, H, T, D, scale, causal, dtype, math_mode, nullptr, 0, true,
                     reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ib200_gemm_bf16(const void* a, const void* b, void* c, const float* bias, int M, int N, int K, int a_transposed,
+                    int b_transposed, ib200_stream_t stream) {
+    return gemm_dispatch(a, b, c, bias, M, N, K, a_transposed, b_transposed, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ib200_linear_fwd(const void* x, const void* w, const float* bias, void* y, int M, int K, int N, ib200_stream_t stream) {
+    return gemm_dispatch(x, w, y, bias, M, N, K, 0, 0, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ib200_linear_bwd(const void* x, const void* w, const void* dy, void* dx, void* dw, float* db, int M, int K, int N,
+                     ib200_stream_t stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (!x || !w || !dy) return IB200_ERR_INVALID_ARGUMENT;
+    int rc = IB200_OK;
+    // dx[M,K] = dy[M,N] w^T: w is stored [K, N], i.e. the "B" of this product stored [N_out = K rows, contraction N contiguous]
+    if (dx && (rc = gemm_dispatch(dy, w, dx, nullptr, M, K, N, 0, 1, stream))) return rc;
+    // dw[K,N] = x^T dy: x is stored [M, K], i.e. the "A" of this product stored [contraction M rows, K contiguous]
+    if (dw && (rc = gemm_dispatch(x, dy, dw, nullptr, K, N, M, 1, 0, stream))) return rc;
+    if (db) {
+        if (N % 8) return IB200_ERR_UNSUPPORTED;
+        colsum_bf16_kernel<<<(N + 63) / 64, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(dy), db, M, N);
+        if (!cuda_ok(cudaGetLastError())) return IB200_ERR_CUDA;
+    }
+    return IB200_OK;
 }
 
 int ib200_attn_check(const void* workspace, ib200_stream_t stream_, int* device_code) {

@@ -21,6 +21,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from . import attention as A
+from . import linear as L
 
 
 def sinusoidal_pe(T: int, C: int, device) -> torch.Tensor:
@@ -37,12 +38,15 @@ class Block(nn.Module):
         super().__init__()
         self.H, self.attn_impl = H, attn_impl
         self.ln1, self.ln2 = nn.LayerNorm(C), nn.LayerNorm(C)
-        self.wqkv, self.wout = nn.Linear(C, 3 * C), nn.Linear(C, C)
+        if attn_impl == "ib200_full":      # projections on this library's tcgen05 GEMM too (weights stored [in, out] like the reference)
+            self.wqkv, self.wout = L.Linear(C, 3 * C), L.Linear(C, C)
+        else:
+            self.wqkv, self.wout = nn.Linear(C, 3 * C), nn.Linear(C, C)
         self.ff1, self.ff2 = nn.Linear(C, 4 * C), nn.Linear(4 * C, C)
 
     def attention(self, x: torch.Tensor) -> torch.Tensor:
         B, T, C = x.shape
-        if self.attn_impl == "ib200_packed":
+        if self.attn_impl in ("ib200_packed", "ib200_full"):
             # the kernels read q, k, v in place inside the projection output and write [B,T,H,D]: no layout copies
             return self.wout(A.causal_attention_packed(self.wqkv(x), self.H))
         q, k, v = self.wqkv(x).split(C, dim=2)
@@ -153,7 +157,7 @@ if __name__ == "__main__":
     ap.add_argument("--heads", type=int, default=12); ap.add_argument("--vocab", type=int, default=8192)
     ap.add_argument("--T", type=int, default=1024); ap.add_argument("--B", type=int, default=16)
     ap.add_argument("--steps", type=int, default=5)
-    ap.add_argument("--attn", default="ib200", choices=["ib200", "ib200_packed"],
-                    help="ib200: dense [B,H,T,D] operands (the reference's layout copies stay); ib200_packed: operands read in place")
+    ap.add_argument("--attn", default="ib200", choices=["ib200", "ib200_packed", "ib200_full"],
+                    help="ib200: dense [B,H,T,D] operands (the reference's layout copies stay); ib200_packed: operands read in place; ib200_full: packed attention plus this library's GEMM for Wqkv / W_out")
     a = ap.parse_args()
     print(json.dumps(run(a.layers, a.d_model, a.heads, a.vocab, a.T, a.B, a.steps, attn_impl=a.attn)))

@@ -36,3 +36,18 @@ def test_insitu_timing_harness_runs():
     from inferno_b200.insitu_gpt import run
     out = run(layers=2, C=256, H=4, vocab=1024, T=512, B=2, steps=2, warmup=1)
     assert out["attn_fwd_ms"] > 0 and out["attn_bwd_main_ms"] > 0 and 0 < out["attn_share_of_step"] < 1
+
+
+def test_full_variant_trains():
+    """Packed attention plus the library's own projection GEMMs inside the training step."""
+    from inferno_b200.insitu_gpt import GPT, train_step
+    torch.manual_seed(0)
+    dev = torch.device("cuda")
+    m = GPT(vocab=512, T=256, C=128, H=2, layers=2, attn_impl="ib200_full").to(dev).to(torch.bfloat16)
+    idx = torch.randint(0, 512, (2, 256), device=dev)
+    tgt = torch.randint(0, 512, (2, 256), device=dev)
+    opt = torch.optim.AdamW(m.parameters(), lr=3e-4)
+    l0 = float(train_step(m, opt, idx, tgt).detach())
+    for _ in range(20):
+        l1 = float(train_step(m, opt, idx, tgt).detach())
+    assert l1 < l0
