@@ -52,36 +52,67 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi polled during the timed region: SM clock under load and throttle reasons."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    """SM clock under load and throttle reasons, read (never set) through NVML every 2 ms on a thread while the timed
+    region runs; falls back to polling nvidia-smi when the NVML binding is missing."""
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
-        self.proc = None
+        self.samples, self.power, self.mask = [], [], 0
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._smi = None
         self.lines = []
+
+    def _nvml_loop(self, nv, handle):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+                self.power.append(nv.nvmlDeviceGetPowerUsage(handle) / 1000.0)
+                self.mask |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(handle))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, text=True)
-            threading.Thread(target=self._pump, daemon=True).start()
+            import pynvml as nv
+            nv.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[self.gpu]) if visible and visible.split(",")[self.gpu].isdigit() else self.gpu
+            handle = nv.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self._thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self._thread.start()
+            return
+        except Exception:
+            self._thread = None
+        try:
+            fields = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+                      "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+                      "clocks_event_reasons.sw_power_cap")
+            self._smi = subprocess.Popen(["nvidia-smi", f"--query-gpu={fields}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "20"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=lambda: [self.lines.append(x.strip()) for x in self._smi.stdout], daemon=True).start()
         except OSError:
-            self.proc = None
-
-    def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self._smi = None
 
     def stop(self):
-        if self.proc is None:
-            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
-        self.proc.terminate()
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+            reasons = sorted(name for name, bit in self.REASONS if self.mask & bit)
+            return dict(sm_mhz=statistics.median(self.samples) if self.samples else None, sm_max_mhz=self.max_mhz,
+                        power_w_max=max(self.power) if self.power else None, samples=len(self.samples), reasons=reasons,
+                        source="nvml")
+        if self._smi is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no clock source available"], samples=0)
+        self._smi.terminate()
         try:
-            self.proc.wait(timeout=5)
+            self._smi.wait(timeout=5)
         except subprocess.TimeoutExpired:
-            self.proc.kill()
+            self._smi.kill()
         sm, smax, reasons, power = [], [], set(), []
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for ln in self.lines:
@@ -96,7 +127,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(smax) if smax else None,
-                    power_w_max=max(power) if power else None, samples=len(sm), reasons=sorted(reasons))
+                    power_w_max=max(power) if power else None, samples=len(sm), reasons=sorted(reasons), source="nvidia-smi")
 
 
 # ----------------------------------------------------------------------------------------------
