@@ -90,6 +90,14 @@ __device__ __forceinline__ void fwd_issue_s(uint32_t tmem_s, uint32_t q_lo, uint
 }
 
 // v_lo_mn: low word of V's MN-major view (lbo = panel stride).
+template <class TR, int K0, int K1>
+__device__ __forceinline__ void fwd_issue_pv_part(uint32_t tmem_o, uint32_t tmem_p, uint32_t v_lo_mn, bool first_tile) {
+    static_assert(!TR::SPLIT, "bf16 mode only");
+#pragma unroll
+    for (int k = K0; k < K1; ++k)
+        umma_ts_f16(tmem_o, tmem_p + k * 8, sdesc_join(v_lo_mn + ((k * 2048) >> 4)), TR::IDESC_PV, (!first_tile || k > 0) ? 1u : 0u);
+}
+
 template <class TR>
 __device__ __forceinline__ void fwd_issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t v_lo_mn, bool first_tile) {
     if constexpr (!TR::SPLIT) {
@@ -126,8 +134,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     uint64_t* v_full = k_empty + KS;        // [KS]
     uint64_t* v_empty = v_full + KS;        // [KS]
     uint64_t* s_full = v_empty + KS;        // [2]
-    uint64_t* p_full = s_full + 2;          // [2]
-    uint64_t* o_full = p_full + 2;          // [2]
+    uint64_t* p_half = s_full + 2;          // [2][2]  P columns 0-63 / 64-127 of tile i are in TMEM
+    uint64_t* o_full = p_half + 4;          // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -151,7 +159,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         *abort_flag = 0;
         mbar_init(q_full, 1);
         for (int s = 0; s < KS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&o_full[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_half[2 * i], 4); mbar_init(&p_half[2 * i + 1], 4); mbar_init(&o_full[i], 1); }
         fence_mbar_init();
     }
     if (warp == 8) { tmem_alloc(tmem_slot, TR::TM_COLS); tmem_relinquish(); }
@@ -209,9 +217,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 mbar_wait(&v_full[sv], (j / KS) & 1, ab, 23);
                 for (int i = 0; i < 2; ++i) {
                     if (j < n_kv[i]) {
-                        mbar_wait(&p_full[i], j & 1, ab, 24);
+                        // P arrives in two halves of 64 key columns: the first k-steps of P.V run under the second half's exponentials
+                        mbar_wait(&p_half[2 * i], j & 1, ab, 24);
                         tc_fence_after_sync();
-                        fwd_issue_pv<TR>(tm_oo[i], tm_s[i], v_lo0 + sv * kStage, j == 0);
+                        if constexpr (!TR::SPLIT) {
+                            fwd_issue_pv_part<TR, 0, TR::PV_KSTEPS / 2>(tm_oo[i], tm_s[i], v_lo0 + sv * kStage, j == 0);
+                            mbar_wait(&p_half[2 * i + 1], j & 1, ab, 25);
+                            tc_fence_after_sync();
+                            fwd_issue_pv_part<TR, TR::PV_KSTEPS / 2, TR::PV_KSTEPS>(tm_oo[i], tm_s[i], v_lo0 + sv * kStage, j == 0);
+                        } else {
+                            mbar_wait(&p_half[2 * i + 1], j & 1, ab, 25);
+                            tc_fence_after_sync();
+                            fwd_issue_pv<TR>(tm_oo[i], tm_s[i], v_lo0 + sv * kStage, j == 0);
+                        }
                         umma_commit(&o_full[i]);
                         if (j + 1 < n_kv[i]) {
                             fwd_issue_s<TR>(tm_s[i], q_addr[i], k_lo0 + sk_next * kStage);
@@ -308,6 +326,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     if constexpr (TR::SPLIT)
                         pl[e >> 1] = pack_bf16x2(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xffff0000u));
                 }
+                if (cc == BN / 2) {
+                    // columns 0-63 were stored a chunk ago: publish them (the wait returns at once)
+                    tmem_wait_st();
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&p_half[2 * i]);
+                }
                 tmem_st_x16(tm_s + (cc >> 1), pk);
                 if constexpr (TR::SPLIT) tmem_st_x16(tm_s + 64 + (cc >> 1), pl);
             }
@@ -321,7 +346,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[i]);
+            if (lane == 0) mbar_arrive(&p_half[2 * i + 1]);
         }
 
         if (nkv > 0) {
