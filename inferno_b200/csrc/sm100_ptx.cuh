@@ -57,11 +57,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking probe.  A thread that is feeding the tensor pipe loses about 70 cycles of issue to a try_wait even
+// when the phase has already completed (try_wait may suspend the thread), and about 4 to a test_wait, so every
+// wait probes with test_wait first and falls back to try_wait only when it really has to wait.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Returns false if the wait was abandoned (abort already raised, or limit hit).
 // The CTA abort flag lives in shared memory; it is polled only every 64th failed try so that
 // spinning warps do not load the shared-memory pipe the MMAs and compute warps depend on.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ab, int site) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_test_wait(bar, parity)) return true;
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -188,6 +202,15 @@ __device__ __forceinline__ void umma_ts_tf32(uint32_t d_tmem, uint32_t a_tmem, u
 // Implies tcgen05.fence::before_thread_sync.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// One lane of a converged warp (elect.sync).  An MMA-issuing warp that stays converged and predicates only the
+// tcgen05.mma / tcgen05.commit instructions on this flag issues an MMA every ~39 cycles and commits almost for free;
+// the same loop run by a single lane inside a divergent branch pays ~44 cycles per MMA and ~44 more per commit.
+__device__ __forceinline__ bool elect_one_lane() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
 }
 
 // ---- descriptors ---------------------------------------------------------------
