@@ -155,6 +155,9 @@ __device__ __forceinline__ void bwd_issue_dq(uint32_t tmem_acc, uint32_t k_lo_mn
     }
 }
 
+template <bool V>
+struct MaskedTag { static constexpr bool value = V; };
+
 template <class TR>
 __global__ void __launch_bounds__(TR::THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_q_lo,
@@ -324,32 +327,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint64_t c2 = pack_f32x2(c, c);
             const float4* v_lse4 = reinterpret_cast<const float4*>(v_lse);
             const float4* v_del4 = reinterpret_cast<const float4*>(v_del);
+            // The masked and the unmasked block are two copies of the loop: a branch inside the loop body would cut it
+            // into one basic block per element pair and expose the full FFMA -> MUFU -> convert latency 16 times.
+            auto body = [&](auto masked_tag) {
+                constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
-            for (int e4 = 0; e4 < 8; ++e4) {
-                const float4 nl = v_lse4[e4], nd = v_del4[e4];   // broadcast 16-byte loads: 4 query columns each
+                for (int e4 = 0; e4 < 8; ++e4) {
+                    const float4 nl = v_lse4[e4], nd = v_del4[e4];   // broadcast 16-byte loads: 4 query columns each
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const int e = e4 * 4 + half * 2;
-                    const uint64_t nl2 = half ? pack_f32x2(nl.z, nl.w) : pack_f32x2(nl.x, nl.y);
-                    const uint64_t nd2 = half ? pack_f32x2(nd.z, nd.w) : pack_f32x2(nd.x, nd.y);
-                    float x0, x1;
-                    unpack_f32x2(ffma2(pack_f32x2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])), c2, nl2), x0, x1);
-                    float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-                    if (masked) {
-                        if (row_dead || (diag && kv_g > q0 + e)) p0 = 0.f;
-                        if (row_dead || (diag && kv_g > q0 + e + 1)) p1 = 0.f;
-                    }
-                    const uint64_t p2 = pack_f32x2(p0, p1);
-                    float d0, d1;
-                    unpack_f32x2(fmul2(p2, fadd2(pack_f32x2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])), nd2)), d0, d1);
-                    pk[e >> 1] = pack_bf16x2(p0, p1);
-                    dk[e >> 1] = pack_bf16x2(d0, d1);
-                    if constexpr (TR::SPLIT) {
-                        pl[e >> 1] = pack_bf16x2(p0 - __uint_as_float(pk[e >> 1] << 16), p1 - __uint_as_float(pk[e >> 1] & 0xffff0000u));
-                        dl[e >> 1] = pack_bf16x2(d0 - __uint_as_float(dk[e >> 1] << 16), d1 - __uint_as_float(dk[e >> 1] & 0xffff0000u));
+                    for (int half = 0; half < 2; ++half) {
+                        const int e = e4 * 4 + half * 2;
+                        const uint64_t nl2 = half ? pack_f32x2(nl.z, nl.w) : pack_f32x2(nl.x, nl.y);
+                        const uint64_t nd2 = half ? pack_f32x2(nd.z, nd.w) : pack_f32x2(nd.x, nd.y);
+                        float x0, x1;
+                        unpack_f32x2(ffma2(pack_f32x2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])), c2, nl2), x0, x1);
+                        float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                        if constexpr (kMasked) {
+                            if (row_dead || (diag && kv_g > q0 + e)) p0 = 0.f;
+                            if (row_dead || (diag && kv_g > q0 + e + 1)) p1 = 0.f;
+                        }
+                        const uint64_t p2 = pack_f32x2(p0, p1);
+                        float d0, d1;
+                        unpack_f32x2(fmul2(p2, fadd2(pack_f32x2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])), nd2)), d0, d1);
+                        pk[e >> 1] = pack_bf16x2(p0, p1);
+                        dk[e >> 1] = pack_bf16x2(d0, d1);
+                        if constexpr (TR::SPLIT) {
+                            pl[e >> 1] = pack_bf16x2(p0 - __uint_as_float(pk[e >> 1] << 16), p1 - __uint_as_float(pk[e >> 1] & 0xffff0000u));
+                            dl[e >> 1] = pack_bf16x2(d0 - __uint_as_float(dk[e >> 1] << 16), d1 - __uint_as_float(dk[e >> 1] & 0xffff0000u));
+                        }
                     }
                 }
-            }
+            };
+            if (masked) body(MaskedTag<true>{}); else body(MaskedTag<false>{});
             tmem_st_x16(t_st, pk);
             if constexpr (!TR::SPLIT) {
                 tmem_st_x16(t_st + 16, dk);
