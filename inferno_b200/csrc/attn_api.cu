@@ -299,11 +299,23 @@ int launch_gemm(const void* a, const void* b, void* c, const float* bias, int M,
     int dev = 0, sms = 148;
     if (cuda_ok(cudaGetDevice(&dev))) (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const long tiles = static_cast<long>((M + TR::BM - 1) / TR::BM) * ((N + TR::BN - 1) / TR::BN);
+    // Split-K when the tiles would leave more than half of the SMs idle and K is long enough to cut: as many slabs as
+    // fit in one wave, each at least eight 64-wide k-slices.  The slabs add into C, so C is zeroed first.
+    const int k_slices = (K + TR::BK - 1) / TR::BK;
+    int splits = 1;
+    if (tiles * 2 <= sms) {
+        splits = static_cast<int>(sms / tiles);
+        if (splits > 8) splits = 8;
+        while (splits > 1 && k_slices / splits < 8) --splits;
+    }
+    if (splits > 1 && !cuda_ok(cudaMemsetAsync(c, 0, static_cast<size_t>(M) * N * 2, stream))) return IB200_ERR_CUDA;
     GemmParams prm;
     prm.bias = bias;
     prm.M = M; prm.N = N; prm.K = K;
+    prm.splits = splits;
     prm.status = nullptr;
-    const int grid = static_cast<int>(tiles < sms ? tiles : sms);       // persistent: one CTA per SM
+    const long units = tiles * splits;
+    const int grid = static_cast<int>(units < sms ? units : sms);       // persistent: one CTA per SM
     gemm_bf16_kernel<A_MN, B_MN><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(ta, tb, tc, prm);
     return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
 }
@@ -500,7 +512,14 @@ int ib200_linear_bwd(const void* x, const void* w, const void* dy, void* dx, voi
     if (dw && (rc = gemm_dispatch(x, dy, dw, nullptr, K, N, M, 1, 0, stream))) return rc;
     if (db) {
         if (N % 8) return IB200_ERR_UNSUPPORTED;
-        colsum_bf16_kernel<<<(N + 63) / 64, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(dy), db, M, N);
+        // row slabs so that the grid covers the SMs a few times over; the slabs meet in fp32 atomics on a zeroed db
+        int slabs = (4 * 148 + (N + 63) / 64 - 1) / ((N + 63) / 64);
+        if (slabs > (M + 255) / 256) slabs = (M + 255) / 256;
+        if (slabs < 1) slabs = 1;
+        const int rows_per_block = ((M + slabs - 1) / slabs + 7) / 8 * 8;
+        if (!cuda_ok(cudaMemsetAsync(db, 0, static_cast<size_t>(N) * 4, stream))) return IB200_ERR_CUDA;
+        colsum_bf16_kernel<<<dim3((N + 63) / 64, (M + rows_per_block - 1) / rows_per_block), 256, 0, stream>>>(
+            static_cast<const __nv_bfloat16*>(dy), db, M, N, rows_per_block);
         if (!cuda_ok(cudaGetLastError())) return IB200_ERR_CUDA;
     }
     return IB200_OK;

@@ -16,6 +16,11 @@
 // ring, one lane of warp 5 issues 128x256x16 tcgen05 MMAs into one of two 256-column TMEM accumulators, and warps 0-3
 // drain the other accumulator (TMEM -> registers -> +bias -> bf16 -> swizzled smem -> TMA store), so the epilogue of a
 // tile overlaps the main loop of the next.
+//
+// Split-K (GemmParams::splits > 1) is for outputs with fewer tiles than SMs and a long K, the weight gradient
+// dW = X^T dY of a projection: the work unit becomes (tile, K slab), every unit adds its partial tile, rounded to bf16,
+// into the zeroed output with a TMA reduction.  The output then carries one bf16 rounding per slab instead of one in
+// all (relative error about 2^-9 * sqrt(slabs + 1)), which is the price of needing no fp32 workspace.
 #pragma once
 
 #include "sm100_ptx.cuh"
@@ -42,6 +47,7 @@ struct GemmTraits {
 struct GemmParams {
     const float* bias;     // [N] fp32 or null
     int M, N, K;
+    int splits;            // >1: the K range is cut into this many slabs; each (tile, slab) unit adds its bf16 partial tile into a zeroed C
     int* status;
 };
 
@@ -67,6 +73,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const int tiles_m = (prm.M + BM - 1) / BM, tiles_n = (prm.N + BN - 1) / BN;
     const int n_tiles = tiles_m * tiles_n;
     const int k_slices = (prm.K + BK - 1) / BK;
+    const int splits = prm.splits > 1 ? prm.splits : 1;
+    const int n_units = n_tiles * splits;                       // unit u: tile u % n_tiles, K slab u / n_tiles
+    const int k_per = (k_slices + splits - 1) / splits;
     AbortCtx ab{abort_flag, prm.status};
 
     if (tid == 0) {
@@ -86,9 +95,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             int it = 0;     // running k-slice count across tiles: ring position
-            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
+                const int tile = unit % n_tiles, ks0 = (unit / n_tiles) * k_per, ks1 = min(k_slices, ks0 + k_per);
                 const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-                for (int ks = 0; ks < k_slices; ++ks, ++it) {
+                for (int ks = ks0; ks < ks1; ++ks, ++it) {
                     const int s = it % NS;
                     mbar_wait(&empty[s], ((it / NS) & 1) ^ 1, ab, 10);
                     mbar_arrive_expect_tx(&full[s], TR::STAGE_BYTES);
@@ -115,11 +125,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(kFmtBF16, BM, BN, A_MN ? kMajorMN : kMajorK, B_MN ? kMajorMN : kMajorK);
             int it = 0, tcount = 0;
-            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
+            for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++tcount) {
+                const int ks0 = (unit / n_tiles) * k_per, ks1 = min(k_slices, ks0 + k_per);
                 const int buf = tcount & 1;
                 mbar_wait(&acc_empty[buf], (((tcount >> 1) & 1) ^ 1), ab, 20);             // epilogue has drained this accumulator
                 tc_fence_after_sync();
-                for (int ks = 0; ks < k_slices; ++ks, ++it) {
+                for (int ks = ks0; ks < ks1; ++ks, ++it) {
                     const int s = it % NS;
                     mbar_wait(&full[s], (it / NS) & 1, ab, 21);
                     tc_fence_after_sync();
@@ -129,7 +140,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     for (int k = 0; k < BK / 16; ++k) {
                         const uint32_t ao = A_MN ? (k * 2048) >> 4 : (k * 32) >> 4;
                         const uint32_t bo = B_MN ? (k * 2048) >> 4 : (k * 32) >> 4;
-                        umma_ss_f16(tmem + buf * BN, sdesc_join(a_lo + ao), sdesc_join(b_lo + bo), idesc, (ks | k) != 0);
+                        umma_ss_f16(tmem + buf * BN, sdesc_join(a_lo + ao), sdesc_join(b_lo + bo), idesc, ((ks - ks0) | k) != 0);
                     }
                     umma_commit(&empty[s]);
                 }
@@ -141,12 +152,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int r = tid;                                           // row inside the tile == TMEM lane
         const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
         int tcount = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
+        for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++tcount) {
+            const int tile = unit % n_tiles;
+            const bool first_slab = unit < n_tiles;                   // the bias goes in once
             const int buf = tcount & 1;
             const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
             // stage this tile's bias slice (zeros where there is no bias or past N)
             float* bias_s = sBias + buf * BN;
-            for (int c = tid; c < BN; c += 128) bias_s[c] = (prm.bias && n0 + c < prm.N) ? prm.bias[n0 + c] : 0.f;
+            for (int c = tid; c < BN; c += 128) bias_s[c] = (prm.bias && first_slab && n0 + c < prm.N) ? prm.bias[n0 + c] : 0.f;
             asm volatile("bar.sync 1, 128;" ::: "memory");
             mbar_wait(&acc_full[buf], (tcount >> 1) & 1, ab, 30);
             tc_fence_after_sync();
@@ -181,7 +194,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 fence_proxy_async_smem();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (tid == 0) {
-                    tma_store_3d(&tm_c, stage, n0 + ch * 64, m0, 0);          // rows / columns past M / N are clipped
+                    if (splits > 1) tma_reduce_add_3d(&tm_c, stage, n0 + ch * 64, m0, 0);   // bf16 add into the zeroed output
+                    else tma_store_3d(&tm_c, stage, n0 + ch * 64, m0, 0);                   // rows / columns past M / N are clipped
                     tma_store_commit();
                 }
             }
@@ -198,14 +212,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 }
 
 // Column sums of a [M, N] bf16 matrix into fp32 (bias gradient: the reference's sum_to_shape after the broadcast add,
-// src/inferno/core/broadcastops.cpp).  One block per 64 columns, 256 threads: 8 row-groups x 32 column-pairs.
-__global__ void __launch_bounds__(256) colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int M, int N) {
+// src/inferno/core/broadcastops.cpp).  Block (x, y): 64 columns, rows y * rows_per_block ...; 256 threads = 8 row-groups
+// x 32 column-pairs; the row slabs are combined with fp32 atomics into `out`, which the host zeroes first.
+__global__ void __launch_bounds__(256) colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int M, int N,
+                                                          int rows_per_block) {
     __shared__ float2 part[8][32];
     const int cp = threadIdx.x & 31, rg = threadIdx.x >> 5;
     const int col = blockIdx.x * 64 + cp * 2;
+    const int row0 = blockIdx.y * rows_per_block, row1 = min(M, row0 + rows_per_block);
     float2 acc = make_float2(0.f, 0.f);
     if (col < N) {
-        for (int row = rg; row < M; row += 8) {
+        for (int row = row0 + rg; row < row1; row += 8) {
             const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(x + static_cast<size_t>(row) * N + col);
             const float2 f = __bfloat1622float2(v);
             acc.x += f.x;
@@ -218,8 +235,8 @@ __global__ void __launch_bounds__(256) colsum_bf16_kernel(const __nv_bfloat16* _
         float2 s = part[0][cp];
 #pragma unroll
         for (int i = 1; i < 8; ++i) { s.x += part[i][cp].x; s.y += part[i][cp].y; }
-        out[col] = s.x;
-        if (col + 1 < N) out[col + 1] = s.y;
+        atomicAdd(out + col, s.x);
+        if (col + 1 < N) atomicAdd(out + col + 1, s.y);
     }
 }
 
