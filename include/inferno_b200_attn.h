@@ -161,6 +161,13 @@ typedef struct CUevent_st* ib200_event_t;
 int ib200_attn_set_timing_events(ib200_event_t fwd_start, ib200_event_t fwd_stop,
                                  ib200_event_t bwd_start, ib200_event_t bwd_stop);
 
+/* Dense casts between fp32 and bf16 (round to nearest even) for callers whose tensors are fp32 but who want the bf16
+ * kernels: the reference has no 16-bit DType (include/inferno/core/dtype.h:17-26; dispatch tags
+ * src/inferno/core/dtype_dispatch.h:43-102), so its tensors reach the bf16 path through these.  n elements, a multiple
+ * of 8; both bases 16-byte aligned.  Asynchronous on `stream`. */
+int ib200_cast_f32_to_bf16(const float* src, void* dst, size_t n, ib200_stream_t stream);
+int ib200_cast_bf16_to_f32(const void* src, float* dst, size_t n, ib200_stream_t stream);
+
 /* Human-readable name of a status value; never NULL. */
 const char* ib200_status_string(int status);
 

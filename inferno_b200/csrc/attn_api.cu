@@ -424,6 +424,35 @@ int ib200_attn_set_timing_events(ib200_event_t fwd_start, ib200_event_t fwd_stop
     return IB200_OK;
 }
 
+static int cast_common(const void* src, void* dst, size_t n) {
+    if (!src || !dst || n == 0) return IB200_ERR_INVALID_ARGUMENT;
+    if (n % 8) return IB200_ERR_UNSUPPORTED;
+    if (!aligned16(src) || !aligned16(dst)) return IB200_ERR_MISALIGNED;
+    return device_ok();
+}
+
+int ib200_cast_f32_to_bf16(const float* src, void* dst, size_t n, ib200_stream_t stream) {
+    const int rc = cast_common(src, dst, n);
+    if (rc != IB200_OK) return rc;
+    const long n8 = static_cast<long>(n / 8);
+    long blocks = n8 / kAuxThreads + 1;
+    if (blocks > kAuxBlocks) blocks = kAuxBlocks;
+    cast_f32_bf16_kernel<<<static_cast<int>(blocks), kAuxThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float4*>(src), static_cast<uint4*>(dst), n8);
+    return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
+}
+
+int ib200_cast_bf16_to_f32(const void* src, float* dst, size_t n, ib200_stream_t stream) {
+    const int rc = cast_common(src, dst, n);
+    if (rc != IB200_OK) return rc;
+    const long n8 = static_cast<long>(n / 8);
+    long blocks = n8 / kAuxThreads + 1;
+    if (blocks > kAuxBlocks) blocks = kAuxBlocks;
+    cast_bf16_f32_kernel<<<static_cast<int>(blocks), kAuxThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(src), reinterpret_cast<float4*>(dst), n8);
+    return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
+}
+
 const char* ib200_status_string(int status) {
     switch (status) {
         case IB200_OK: return "ok";

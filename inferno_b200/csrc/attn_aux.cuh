@@ -65,6 +65,26 @@ inline int launch_split_bf16(const float* in, void* hi, void* lo, const RowLayou
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 
+// Dense casts between fp32 and bf16 (round to nearest even), 8 elements per thread: for callers whose tensors are
+// fp32 (the reference has no 16-bit DType, include/inferno/core/dtype.h:17-26) but who run the bf16 kernels.
+__global__ void __launch_bounds__(kAuxThreads) cast_f32_bf16_kernel(const float4* __restrict__ in, uint4* __restrict__ out, long n8) {
+    for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
+        const float4 a = in[2 * i], b = in[2 * i + 1];
+        const __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+        const __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+        out[i] = make_uint4(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1),
+                            *reinterpret_cast<const uint32_t*>(&p2), *reinterpret_cast<const uint32_t*>(&p3));
+    }
+}
+
+__global__ void __launch_bounds__(kAuxThreads) cast_bf16_f32_kernel(const uint4* __restrict__ in, float4* __restrict__ out, long n8) {
+    for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
+        const uint4 v = in[i];
+        out[2 * i] = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+        out[2 * i + 1] = make_float4(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u), __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
+    }
+}
+
 // One row of D elements is covered by TPR threads, each loading 16 bytes of O and of dO.
 // Outputs are laid out [heads, T_pad] with T_pad a multiple of 64 so that the backward kernel can
 // fetch the 64 values of a query block with one aligned bulk copy; both are stored negated and

@@ -32,9 +32,14 @@ void check(int rc, const char* what) {
     if (rc != IB200_OK) fail(std::string(what) + ": " + ib200_status_string(rc));
 }
 
+// Raw device storage for n bf16 values, allocated like any other Inferno tensor (two bf16 per Float32 element).
+Tensor make_bf16_buffer(size_t n, const char* name, const Device& dev) {
+    return Tensor(DType::Float32, std::vector<size_t>{n / 2 + 8}, name, dev);
+}
+
 }  // namespace
 
-Tensor causal_attention(const Tensor& q_in, const Tensor& k_in, const Tensor& v_in, float scale) {
+Tensor causal_attention(const Tensor& q_in, const Tensor& k_in, const Tensor& v_in, float scale, AttentionMath math) {
     if (q_in.device() != k_in.device() || q_in.device() != v_in.device()) fail("tensors are on different devices");
     if (q_in.ndim() != 4 || q_in.shape() != k_in.shape() || q_in.shape() != v_in.shape()) fail("expects q, k, v of equal shape [B, H, T, D]");
     if (q_in.dtype() != DType::Float32 || k_in.dtype() != DType::Float32 || v_in.dtype() != DType::Float32) fail("expects Float32 tensors");
@@ -50,46 +55,81 @@ Tensor causal_attention(const Tensor& q_in, const Tensor& k_in, const Tensor& v_
     Tensor q = q_in.contiguous(), k = k_in.contiguous(), v = v_in.contiguous();
     const auto& shp = q.shape();
     const int B = static_cast<int>(shp[0]), H = static_cast<int>(shp[1]), T = static_cast<int>(shp[2]), D = static_cast<int>(shp[3]);
+    const size_t n = q.numel();
+    const bool bf16 = math == AttentionMath::BFloat16;
+    const int dtype = bf16 ? IB200_DTYPE_BF16 : IB200_DTYPE_F32;
 
     const bool gradreq = grad_enabled && (q_in.requires_grad() || k_in.requires_grad() || v_in.requires_grad());
     Tensor out(DType::Float32, shp, "attention", q.device(), gradreq);
     Tensor lse(DType::Float32, std::vector<size_t>{shp[0], shp[1], shp[2]}, "attention_lse", q.device());
 
+    // what the kernels read and write: the tensors themselves, or bf16 copies of them
+    Tensor sq = q, sk = k, sv = v, sout = out;
+    if (bf16) {
+        sq = make_bf16_buffer(n, "attention_q_bf16", q.device());
+        sk = make_bf16_buffer(n, "attention_k_bf16", q.device());
+        sv = make_bf16_buffer(n, "attention_v_bf16", q.device());
+        sout = make_bf16_buffer(n, "attention_out_bf16", q.device());
+        check(ib200_cast_f32_to_bf16(dev_ptr(q), dev_ptr(sq), n, nullptr), "cast q");
+        check(ib200_cast_f32_to_bf16(dev_ptr(k), dev_ptr(sk), n, nullptr), "cast k");
+        check(ib200_cast_f32_to_bf16(dev_ptr(v), dev_ptr(sv), n, nullptr), "cast v");
+    }
+
     size_t ws_bytes = 0;
-    check(ib200_attn_workspace_bytes(B, H, T, D, IB200_DTYPE_F32, IB200_PASS_FWD, &ws_bytes), "workspace query");
+    check(ib200_attn_workspace_bytes(B, H, T, D, dtype, IB200_PASS_FWD, &ws_bytes), "workspace query");
     Tensor ws = make_workspace(ws_bytes, q.device());
     // the reference launches everything on the legacy default stream
-    check(ib200_attn_fwd(dev_ptr(q), dev_ptr(k), dev_ptr(v), dev_ptr(out), dev_ptr(lse), B, H, T, D, scale, /*causal=*/1,
-                         IB200_DTYPE_F32, IB200_MATH_TF32, dev_ptr(ws), ws_bytes, nullptr),
+    check(ib200_attn_fwd(dev_ptr(sq), dev_ptr(sk), dev_ptr(sv), dev_ptr(sout), dev_ptr(lse), B, H, T, D, scale, /*causal=*/1,
+                         dtype, IB200_MATH_TF32, dev_ptr(ws), ws_bytes, nullptr),
           "forward");
+    if (bf16) check(ib200_cast_bf16_to_f32(dev_ptr(sout), dev_ptr(out), n, nullptr), "widen y");
     int code = 0;
     check(ib200_attn_check(dev_ptr(ws), nullptr, &code), "forward (device status)");
 
-    if (gradreq) GetImpl(out)->gradfn() = std::make_shared<AttentionBackward>(q_in, k_in, v_in, out, lse, scale);
+    if (gradreq) GetImpl(out)->gradfn() = std::make_shared<AttentionBackward>(q_in, k_in, v_in, sq, sk, sv, sout, lse, scale, math);
     return out;
 }
 
-AttentionBackward::AttentionBackward(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& lse, float scale)
-    : m_q(q), m_k(k), m_v(v), m_out(out), m_lse(lse), m_scale(scale) {
+AttentionBackward::AttentionBackward(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& sq, const Tensor& sk, const Tensor& sv,
+                                     const Tensor& sout, const Tensor& lse, float scale, AttentionMath math)
+    : m_q(q), m_k(k), m_v(v), m_sq(sq), m_sk(sk), m_sv(sv), m_sout(sout), m_lse(lse), m_scale(scale), m_math(math) {
     set_name("AttentionBackward");
 }
 
 void AttentionBackward::backward() {
     NoGradGuard guard;
     Tensor g_out = Engine::grad_in(this, 0).contiguous();
-    Tensor q = m_q.contiguous(), k = m_k.contiguous(), v = m_v.contiguous();
-    const auto& shp = q.shape();
+    const auto& shp = m_q.shape();
     const int B = static_cast<int>(shp[0]), H = static_cast<int>(shp[1]), T = static_cast<int>(shp[2]), D = static_cast<int>(shp[3]);
+    const size_t n = m_q.numel();
+    const bool bf16 = m_math == AttentionMath::BFloat16;
+    const int dtype = bf16 ? IB200_DTYPE_BF16 : IB200_DTYPE_F32;
+    const Device dev = m_q.device();
+    // Float32 mode saved the inputs themselves; they may have been views, so make them dense again
+    Tensor sq = bf16 ? m_sq : m_sq.contiguous(), sk = bf16 ? m_sk : m_sk.contiguous(), sv = bf16 ? m_sv : m_sv.contiguous();
 
-    Tensor dq(DType::Float32, shp, "attention_dq", q.device());
-    Tensor dk(DType::Float32, shp, "attention_dk", q.device());
-    Tensor dv(DType::Float32, shp, "attention_dv", q.device());
+    Tensor dq(DType::Float32, shp, "attention_dq", dev);
+    Tensor dk(DType::Float32, shp, "attention_dk", dev);
+    Tensor dv(DType::Float32, shp, "attention_dv", dev);
+    Tensor sdo = g_out, sdq = dq, sdk = dk, sdv = dv;
+    if (bf16) {
+        sdo = make_bf16_buffer(n, "attention_do_bf16", dev);
+        sdq = make_bf16_buffer(n, "attention_dq_bf16", dev);
+        sdk = make_bf16_buffer(n, "attention_dk_bf16", dev);
+        sdv = make_bf16_buffer(n, "attention_dv_bf16", dev);
+        check(ib200_cast_f32_to_bf16(dev_ptr(g_out), dev_ptr(sdo), n, nullptr), "cast dO");
+    }
     size_t ws_bytes = 0;
-    check(ib200_attn_workspace_bytes(B, H, T, D, IB200_DTYPE_F32, IB200_PASS_BWD, &ws_bytes), "workspace query");
-    Tensor ws = make_workspace(ws_bytes, q.device());
-    check(ib200_attn_bwd(dev_ptr(q), dev_ptr(k), dev_ptr(v), dev_ptr(m_out), dev_ptr(g_out), dev_ptr(m_lse), dev_ptr(dq), dev_ptr(dk),
-                         dev_ptr(dv), B, H, T, D, m_scale, 1, IB200_DTYPE_F32, IB200_MATH_TF32, dev_ptr(ws), ws_bytes, nullptr),
+    check(ib200_attn_workspace_bytes(B, H, T, D, dtype, IB200_PASS_BWD, &ws_bytes), "workspace query");
+    Tensor ws = make_workspace(ws_bytes, dev);
+    check(ib200_attn_bwd(dev_ptr(sq), dev_ptr(sk), dev_ptr(sv), dev_ptr(m_sout), dev_ptr(sdo), dev_ptr(m_lse), dev_ptr(sdq), dev_ptr(sdk),
+                         dev_ptr(sdv), B, H, T, D, m_scale, 1, dtype, IB200_MATH_TF32, dev_ptr(ws), ws_bytes, nullptr),
           "backward");
+    if (bf16) {
+        check(ib200_cast_bf16_to_f32(dev_ptr(sdq), dev_ptr(dq), n, nullptr), "widen dq");
+        check(ib200_cast_bf16_to_f32(dev_ptr(sdk), dev_ptr(dk), n, nullptr), "widen dk");
+        check(ib200_cast_bf16_to_f32(dev_ptr(sdv), dev_ptr(dv), n, nullptr), "widen dv");
+    }
     int code = 0;
     check(ib200_attn_check(dev_ptr(ws), nullptr, &code), "backward (device status)");
 
@@ -106,7 +146,10 @@ void AttentionBackward::release() {
     m_q = Tensor{};
     m_k = Tensor{};
     m_v = Tensor{};
-    m_out = Tensor{};
+    m_sq = Tensor{};
+    m_sk = Tensor{};
+    m_sv = Tensor{};
+    m_sout = Tensor{};
     m_lse = Tensor{};
 }
 

@@ -14,22 +14,34 @@
 
 namespace Inferno {
 
+// Arithmetic of the fused op.  The tensors are Float32 either way (the reference has no 16-bit DType,
+// include/inferno/core/dtype.h:17-26):
+//   Float32   fp32 operands (carried as bf16 hi + lo pairs on the tensor cores, error ~1e-5); head dim 64
+//   BFloat16  q, k, v and the upstream gradient are rounded to bf16 on the device, the bf16 kernels run (head dim 64
+//             or 128, fp32 accumulation), and y / dq / dk / dv are widened back to Float32: the tolerance is the bf16
+//             one (2e-2 normwise), the saved activations take half the memory and the kernels run several times faster
+enum class AttentionMath { Float32, BFloat16 };
+
 // y = softmax(mask(q k^T * scale)) v with a causal mask.  Attaches an AttentionBackward node to y
 // when gradients are enabled and any input requires them.  Errors follow the reference's
 // convention (log + exit(1), src/inferno/core/ops.cpp:44-47).
-Tensor causal_attention(const Tensor& q, const Tensor& k, const Tensor& v, float scale);
+Tensor causal_attention(const Tensor& q, const Tensor& k, const Tensor& v, float scale, AttentionMath math = AttentionMath::Float32);
 
 // Backward node of causal_attention (interface: src/inferno/gradfn/node.h:23-45).
 class AttentionBackward : public Node {
 public:
-    AttentionBackward(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& lse, float scale);
+    // q, k, v: the op's inputs (graph edges).  sq, sk, sv, sout: what the backward kernels read - the same tensors in
+    // Float32 mode, bf16 copies (raw storage) in BFloat16 mode.
+    AttentionBackward(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& sq, const Tensor& sk, const Tensor& sv,
+                      const Tensor& sout, const Tensor& lse, float scale, AttentionMath math);
     void backward() override;
     void release() override;
     void get_inputs(std::vector<Tensor>& out) const override;
 
 private:
-    Tensor m_q, m_k, m_v, m_out, m_lse;
+    Tensor m_q, m_k, m_v, m_sq, m_sk, m_sv, m_sout, m_lse;
     float m_scale;
+    AttentionMath m_math;
 };
 
 }  // namespace Inferno

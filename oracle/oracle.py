@@ -51,8 +51,11 @@ def rel_err(x: np.ndarray, ref: np.ndarray) -> float:
     return float(num / den) if den > 0 else float(num)
 
 
-def ref_attention(q, k, v, dO=None, device: str = "cpu"):
-    """Run the compiled reference.  Returns (o, dq, dk, dv, timings); grads are None if dO is None."""
+def ref_attention(q, k, v, dO=None, device: str = "cpu", single_pass: bool = False):
+    """Run the compiled reference.  Returns (o, dq, dk, dv, timings); grads are None if dO is None.
+
+    ``single_pass`` runs the backward as one engine pass through the autograd additions of
+    inferno_b200/inferno_shim/autograd_patches.h instead of the two-stage workaround."""
     if not have_ref():
         raise RuntimeError("oracle/_ref/ref_attention is not built (run `make -C oracle ref` where the reference is present)")
     B, H, T, D = q.shape
@@ -64,7 +67,7 @@ def ref_attention(q, k, v, dO=None, device: str = "cpu"):
                 np.ascontiguousarray(arr, dtype=np.float32).tofile(paths[name])
         prefix = os.path.join(td, "out")
         cmd = [REF_BIN, device, str(B), str(H), str(T), str(D), paths["q"], paths["k"], paths["v"], paths["do"], prefix,
-               "0" if dO is not None else "1"]
+               ("2" if single_pass else "0") if dO is not None else "1"]
         res = subprocess.run(cmd, check=True, capture_output=True, text=True, cwd=td)
         timings = json.loads(res.stdout.strip().splitlines()[-1])
         rd = lambda s: np.fromfile(prefix + "." + s + ".bin", dtype=np.float32).reshape(B, H, T, D)

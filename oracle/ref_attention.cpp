@@ -17,7 +17,11 @@
 // Engine::backward always seeds ones (src/inferno/gradengine/engine.cpp:59),
 // which is why the upstream gradient enters through a multiply.
 //
-// Usage: ref_attention <cpu|cuda> B H T D q.bin k.bin v.bin do.bin out_prefix [fwd_only]
+// With a fourth mode argument of 2 the same composition is run through the autograd additions of
+// inferno_b200/inferno_shim/autograd_patches.h (masked_fill and contiguous that stay in the graph, a seeded backward)
+// and a single backward pass; tests compare the two.
+//
+// Usage: ref_attention <cpu|cuda> B H T D q.bin k.bin v.bin do.bin out_prefix [mode: 0 fwd+bwd, 1 fwd only, 2 single-pass bwd]
 // Files are raw little-endian fp32, dense row-major [B,H,T,D].
 // Writes <out_prefix>.{o,dq,dk,dv}.bin and prints one JSON line with timings.
 #include <chrono>
@@ -32,6 +36,7 @@
 #include <inferno/core/ops.h>
 #include "inferno/core/ops_impl.h"
 #include "inferno/core/tensorimpl.h"
+#include "../inferno_b200/inferno_shim/autograd_patches.h"
 
 using Inferno::Tensor;
 
@@ -70,7 +75,8 @@ int main(int argc, char** argv) {
     const size_t T = std::strtoul(argv[4], nullptr, 10), D = std::strtoul(argv[5], nullptr, 10);
     const size_t n = B * H * T * D;
     const std::string prefix = argv[10];
-    const bool fwd_only = argc > 11 && std::atoi(argv[11]) != 0;
+    const int mode = argc > 11 ? std::atoi(argv[11]) : 0;
+    const bool fwd_only = mode == 1, single_pass = mode == 2;
     Inferno::Device dev = on_cuda ? Inferno::Device::cuda(0) : Inferno::Device::cpu();
 
     std::vector<float> hq = read_bin(argv[6], n), hk = read_bin(argv[7], n), hv = read_bin(argv[8], n);
@@ -83,7 +89,7 @@ int main(int argc, char** argv) {
 
     // ---- forward (InfernoApp/main.cpp:737-754) ----
     double t0 = now_ms();
-    Tensor kt = k.transpose(-1, -2).contiguous();
+    Tensor kt = single_pass ? Inferno::contiguous_with_grad(k.transpose(-1, -2)) : k.transpose(-1, -2).contiguous();
     kt.set_requires_grad(true);  // re-arm cut #1 (ContiguousBackward is attached but unreachable otherwise)
     Tensor s0 = Inferno::matmul(q, kt, "QK^T");
     const float scale = 1.0f / std::sqrt(static_cast<float>(D));
@@ -91,8 +97,8 @@ int main(int argc, char** argv) {
     std::vector<int> ones_data(T * T, 1);
     Tensor ones(Inferno::DType::Int32, ones_data, {1, 1, T, T}, "causal_mask_ones", dev);
     Tensor mask = Inferno::triu(ones, 1);
-    Tensor sm = Inferno::masked_fill(s1, mask, -1e9f);
-    sm.set_requires_grad(true);  // re-arm cut #2: sm becomes a leaf, stage boundary
+    Tensor sm = single_pass ? Inferno::masked_fill_with_grad(s1, mask, -1e9f) : Inferno::masked_fill(s1, mask, -1e9f);
+    if (!single_pass) sm.set_requires_grad(true);  // re-arm cut #2: sm becomes a leaf, stage boundary
     Tensor p = Inferno::Softmax(sm, -1);
     Tensor y = Inferno::matmul(p, v, "attn@V");
     if (on_cuda) { (void)y.to(Inferno::Device::cpu()); }  // device->host read = completion point
@@ -102,6 +108,17 @@ int main(int argc, char** argv) {
     double t2 = t1, t3 = t1;
     if (!fwd_only) {
         t2 = now_ms();
+        if (single_pass) {
+            Inferno::backward_with_seed(y, dO);  // one pass through MaskedFillBackward and the re-armed ContiguousBackward
+            if (!q.grad() || !k.grad() || !v.grad()) { std::fprintf(stderr, "missing gradient\n"); return 3; }
+            write_tensor(prefix + ".dq.bin", q.Getgrad().contiguous(), n);
+            write_tensor(prefix + ".dk.bin", k.Getgrad().contiguous(), n);
+            write_tensor(prefix + ".dv.bin", v.Getgrad().contiguous(), n);
+            t3 = now_ms();
+            std::printf("{\"device\": \"%s\", \"B\": %zu, \"H\": %zu, \"T\": %zu, \"D\": %zu, \"fwd_ms\": %.3f, \"bwd_ms\": %.3f, \"single_pass\": true}\n",
+                        argv[1], B, H, T, D, t1 - t0, t3 - t2);
+            return 0;
+        }
         Tensor l1 = y * dO;
         l1.backward();  // stage 1: dV and dS
         if (!sm.grad()) { std::fprintf(stderr, "stage 1 produced no dS\n"); return 3; }

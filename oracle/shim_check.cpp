@@ -2,7 +2,8 @@
 // the reference's own headers and objects, run on Device::cuda(0), and its gradients are produced by the
 // reference's autograd Engine walking the AttentionBackward node (seeded through a multiply, because
 // Engine::backward always seeds ones, src/inferno/gradengine/engine.cpp:59).
-// Usage: shim_check B H T D q.bin k.bin v.bin do.bin out_prefix   -> writes <prefix>.{o,dq,dk,dv}.bin
+// Usage: shim_check B H T D q.bin k.bin v.bin do.bin out_prefix [bf16]   -> writes <prefix>.{o,dq,dk,dv}.bin
+// With the trailing "bf16" the op runs in AttentionMath::BFloat16 (Float32 tensors, bf16 kernels).
 #include <cstdio>
 #include <cstdlib>
 #include <string>
@@ -44,7 +45,9 @@ int main(int argc, char** argv) {
     Tensor v(Inferno::DType::Float32, hv, {B, H, T, D}, "v", dev, true);
     Tensor dO(Inferno::DType::Float32, hdo, {B, H, T, D}, "dO", dev, false);
 
-    Tensor y = Inferno::causal_attention(q, k, v, 1.0f / std::sqrt(static_cast<float>(D)));
+    const bool bf16 = argc > 10 && std::string(argv[10]) == "bf16";
+    Tensor y = Inferno::causal_attention(q, k, v, 1.0f / std::sqrt(static_cast<float>(D)),
+                                         bf16 ? Inferno::AttentionMath::BFloat16 : Inferno::AttentionMath::Float32);
     write_tensor(prefix + ".o.bin", y, n);
     Tensor loss = y * dO;          // MultiplyBackward hands dO to AttentionBackward
     loss.backward();

@@ -101,6 +101,18 @@ def test_backward_argument_validation(built_lib):
     assert bwd(p, ws_bytes=256) == _capi.ERR_WORKSPACE
 
 
+def test_cast_argument_validation(built_lib):
+    """fp32 <-> bf16 casts: host-side rejection before any CUDA call (fake addresses, never dereferenced)."""
+    L = _capi.lib()
+    assert L.ib200_cast_f32_to_bf16(None, 0x20000, 16, None) == _capi.ERR_INVALID_ARGUMENT
+    assert L.ib200_cast_bf16_to_f32(0x10000, 0x20000, 0, None) == _capi.ERR_INVALID_ARGUMENT
+    assert L.ib200_cast_f32_to_bf16(0x10000, 0x20000, 12, None) == _capi.ERR_UNSUPPORTED        # not a multiple of 8
+    assert L.ib200_cast_bf16_to_f32(0x10004, 0x20000, 16, None) == _capi.ERR_MISALIGNED
+    import torch
+    if not torch.cuda.is_available():      # valid arguments: only ever issued where there is no GPU to run them on
+        assert L.ib200_cast_f32_to_bf16(0x10000, 0x20000, 16, None) == _capi.ERR_NO_DEVICE
+
+
 def test_no_device_fails_loudly(built_lib):
     """With well-formed arguments and no sm_100 device the call reports it; nothing else runs."""
     import torch

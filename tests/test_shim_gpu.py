@@ -16,13 +16,13 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SHIM = os.path.join(ROOT, "oracle", "_ref", "shim_check")
 
 
-def run_binary(binary, args, q, k, v, do):
+def run_binary(binary, args, q, k, v, do, tail=()):
     B, H, T, D = q.shape
     with tempfile.TemporaryDirectory() as td:
         for name, arr in (("q", q), ("k", k), ("v", v), ("do", do)):
             np.ascontiguousarray(arr, dtype=np.float32).tofile(os.path.join(td, name + ".bin"))
         prefix = os.path.join(td, "out")
-        cmd = [binary] + args + [str(B), str(H), str(T), str(D)] + [os.path.join(td, n + ".bin") for n in ("q", "k", "v", "do")] + [prefix]
+        cmd = [binary] + args + [str(B), str(H), str(T), str(D)] + [os.path.join(td, n + ".bin") for n in ("q", "k", "v", "do")] + [prefix] + list(tail)
         subprocess.run(cmd, check=True, cwd=td, capture_output=True, timeout=300)
         return [np.fromfile(f"{prefix}.{s}.bin", dtype=np.float32).reshape(B, H, T, D) for s in ("o", "dq", "dk", "dv")]
 
@@ -40,6 +40,20 @@ def test_inferno_idiom_op_and_engine_backward(oracle_mod, shape):
     for name, x, r in zip(("O", "dQ", "dK", "dV"), outs, refs):
         err = oracle_mod.rel_err(x, r)
         assert err < 1e-3, f"{name}: rel err {err:.3e}"
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 200, 64), (2, 2, 384, 128)])
+def test_inferno_idiom_op_bf16_math(oracle_mod, shape):
+    """AttentionMath::BFloat16: Float32 Inferno tensors in and out, bf16 kernels in between (the only way the
+    reference's tensors reach head dim 128); parity with the fp64 evaluator at the bf16 tolerance."""
+    if not os.path.isfile(SHIM):
+        pytest.skip("oracle/_ref/shim_check not built (reference sources absent at build time)")
+    q, k, v, do = make_inputs(*shape, 43)
+    outs = run_binary(SHIM, [], q, k, v, do, tail=["bf16"])
+    refs = oracle_mod.attn_fp64(q, k, v, do)
+    for name, x, r in zip(("O", "dQ", "dK", "dV"), outs, refs):
+        err = oracle_mod.rel_err(x, r)
+        assert err < 2e-2, f"{name}: rel err {err:.3e}"
 
 
 def test_against_the_reference_cuda_path(oracle_mod):
