@@ -72,45 +72,45 @@ __device__ __forceinline__ constexpr int split_b(int t) { return t == 2 ? 1 : 0;
 
 // The issue helpers take descriptor LOW WORDS (sdesc_lo) so that each MMA costs one 32-bit add per operand.
 template <class TR>
-__device__ __forceinline__ void fwd_issue_s(uint32_t tmem_s, uint32_t q_lo, uint32_t k_lo) {
+__device__ __forceinline__ void fwd_issue_s(uint32_t tmem_s, uint32_t q_lo, uint32_t k_lo, bool leader) {
     if constexpr (!TR::SPLIT) {
 #pragma unroll
         for (int k = 0; k < TR::D / 16; ++k) {
             const uint32_t off = ((k / 4) * TR::PANEL_BYTES + (k % 4) * 32) >> 4;
-            umma_ss_f16(tmem_s, sdesc_join(q_lo + off), sdesc_join(k_lo + off), TR::IDESC_S, k > 0);
+            if (leader) umma_ss_f16(tmem_s, sdesc_join(q_lo + off), sdesc_join(k_lo + off), TR::IDESC_S, k > 0);
         }
     } else {
 #pragma unroll
         for (int t = 0; t < 3; ++t)
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-                umma_ss_f16(tmem_s, sdesc_join(q_lo + ((split_a(t) * TR::PANEL_BYTES + k * 32) >> 4)),
+                if (leader) umma_ss_f16(tmem_s, sdesc_join(q_lo + ((split_a(t) * TR::PANEL_BYTES + k * 32) >> 4)),
                             sdesc_join(k_lo + ((split_b(t) * TR::PANEL_BYTES + k * 32) >> 4)), TR::IDESC_S, (t | k) != 0);
     }
 }
 
 // v_lo_mn: low word of V's MN-major view (lbo = panel stride).
 template <class TR, int K0, int K1>
-__device__ __forceinline__ void fwd_issue_pv_part(uint32_t tmem_o, uint32_t tmem_p, uint32_t v_lo_mn, bool first_tile) {
+__device__ __forceinline__ void fwd_issue_pv_part(uint32_t tmem_o, uint32_t tmem_p, uint32_t v_lo_mn, bool first_tile, bool leader) {
     static_assert(!TR::SPLIT, "bf16 mode only");
 #pragma unroll
     for (int k = K0; k < K1; ++k)
-        umma_ts_f16(tmem_o, tmem_p + k * 8, sdesc_join(v_lo_mn + ((k * 2048) >> 4)), TR::IDESC_PV, (!first_tile || k > 0) ? 1u : 0u);
+        if (leader) umma_ts_f16(tmem_o, tmem_p + k * 8, sdesc_join(v_lo_mn + ((k * 2048) >> 4)), TR::IDESC_PV, (!first_tile || k > 0) ? 1u : 0u);
 }
 
 template <class TR>
-__device__ __forceinline__ void fwd_issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t v_lo_mn, bool first_tile) {
+__device__ __forceinline__ void fwd_issue_pv(uint32_t tmem_o, uint32_t tmem_p, uint32_t v_lo_mn, bool first_tile, bool leader) {
     if constexpr (!TR::SPLIT) {
 #pragma unroll
         for (int k = 0; k < TR::PV_KSTEPS; ++k)
-            umma_ts_f16(tmem_o, tmem_p + k * 8, sdesc_join(v_lo_mn + ((k * 2048) >> 4)), TR::IDESC_PV, (!first_tile || k > 0) ? 1u : 0u);
+            if (leader) umma_ts_f16(tmem_o, tmem_p + k * 8, sdesc_join(v_lo_mn + ((k * 2048) >> 4)), TR::IDESC_PV, (!first_tile || k > 0) ? 1u : 0u);
     } else {
         // P_hi in columns 0-63, P_lo in columns 64-127 of the S region; V_hi / V_lo are the two panels
 #pragma unroll
         for (int t = 0; t < 3; ++t)
 #pragma unroll
             for (int k = 0; k < TR::PV_KSTEPS; ++k)
-                umma_ts_f16(tmem_o, tmem_p + split_a(t) * 64 + k * 8, sdesc_join(v_lo_mn + ((split_b(t) * TR::PANEL_BYTES + k * 2048) >> 4)),
+                if (leader) umma_ts_f16(tmem_o, tmem_p + split_a(t) * 64 + k * 8, sdesc_join(v_lo_mn + ((split_b(t) * TR::PANEL_BYTES + k * 2048) >> 4)),
                             TR::IDESC_PV, (!first_tile || (t | k) != 0) ? 1u : 0u);
     }
 }
@@ -128,14 +128,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     uint8_t* sK = sQ + 2 * TR::TILE_BYTES;                // KS tiles
     uint8_t* sV = sK + KS * TR::TILE_BYTES;               // KS tiles
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + KS * TR::TILE_BYTES);
-    uint64_t* q_full = bars;                // [1]
-    uint64_t* k_full = bars + 1;            // [KS]
-    uint64_t* k_empty = k_full + KS;        // [KS]
-    uint64_t* v_full = k_empty + KS;        // [KS]
-    uint64_t* v_empty = v_full + KS;        // [KS]
-    uint64_t* s_full = v_empty + KS;        // [2]
+    uint64_t* q_full = bars;                // [1]   query tiles + K_0
+    uint64_t* k0_free = bars + 1;           // [1]   the first S MMAs have read K_0
+    uint64_t* kv_full = bars + 2;           // [KS]  load group j: K_{j+1} and V_j
+    uint64_t* kv_empty = kv_full + KS;      // [KS]
+    uint64_t* s_full = kv_empty + KS;       // [2]   S_i is in TMEM (and every MMA issued before it has completed)
     uint64_t* p_half = s_full + 2;          // [2][2]  P columns 0-63 / 64-127 of tile i are in TMEM
-    uint64_t* o_full = p_half + 4;          // [2]
+    uint64_t* o_full = p_half + 4;          // [2]   after the last P.V of tile i
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -158,7 +157,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (tid == 0) {
         *abort_flag = 0;
         mbar_init(q_full, 1);
-        for (int s = 0; s < KS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+        mbar_init(k0_free, 1);
+        for (int s = 0; s < KS; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_half[2 * i], 4); mbar_init(&p_half[2 * i + 1], 4); mbar_init(&o_full[i], 1); }
         fence_mbar_init();
     }
@@ -176,69 +176,82 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     if (warp == 9) {
         // ------------------------------ TMA producer ------------------------------
+        // Load group j = {K_{j+1}, V_j}: exactly what iteration j of the MMA issuer consumes (P.V_j, then S = Q K_{j+1}^T),
+        // so a group needs one full and one empty barrier.  K_j lives in K slot j % KS, V_j in V slot j % KS; K_0 comes
+        // with the query tiles.
         if (lane == 0) {
             const int q_tiles = (n_kv[1] > 0) ? 2 : 1;
-            mbar_arrive_expect_tx(q_full, q_tiles * TR::TILE_BYTES);
+            mbar_arrive_expect_tx(q_full, (q_tiles + 1) * TR::TILE_BYTES);
             for (int i = 0; i < q_tiles; ++i)
                 for (int p = 0; p < TR::NP; ++p)
                     tma_load_4d(sQ + i * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_q_lo : &tm_q, q_full, TR::SPLIT ? 0 : p * 64, m_tile[i] * BM, hd, bt);
+            for (int p = 0; p < TR::NP; ++p)
+                tma_load_4d(sK + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_k_lo : &tm_k, q_full, TR::SPLIT ? 0 : p * 64, 0, hd, bt);
             for (int j = 0; j < n_iter; ++j) {
                 const int s = j % KS;
-                const uint32_t ph = (j / KS) & 1;
-                mbar_wait(&k_empty[s], ph ^ 1, ab, 10);
-                mbar_arrive_expect_tx(&k_full[s], TR::TILE_BYTES);
+                const bool has_k = (j + 1) < n_iter;
+                mbar_wait(&kv_empty[s], ((j / KS) & 1) ^ 1, ab, 10);
+                if (j == KS - 1) mbar_wait(k0_free, 0, ab, 11);            // K_KS reuses the slot of K_0
+                mbar_arrive_expect_tx(&kv_full[s], (has_k ? 2 : 1) * TR::TILE_BYTES);
+                if (has_k)
+                    for (int p = 0; p < TR::NP; ++p)
+                        tma_load_4d(sK + ((j + 1) % KS) * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_k_lo : &tm_k, &kv_full[s],
+                                    TR::SPLIT ? 0 : p * 64, (j + 1) * BN, hd, bt);
                 for (int p = 0; p < TR::NP; ++p)
-                    tma_load_4d(sK + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_k_lo : &tm_k, &k_full[s], TR::SPLIT ? 0 : p * 64, j * BN, hd, bt);
-                mbar_wait(&v_empty[s], ph ^ 1, ab, 11);
-                mbar_arrive_expect_tx(&v_full[s], TR::TILE_BYTES);
-                for (int p = 0; p < TR::NP; ++p)
-                    tma_load_4d(sV + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_v_lo : &tm_v, &v_full[s], TR::SPLIT ? 0 : p * 64, j * BN, hd, bt);
+                    tma_load_4d(sV + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_v_lo : &tm_v, &kv_full[s], TR::SPLIT ? 0 : p * 64, j * BN, hd, bt);
             }
         }
     } else if (warp == 8) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0 && n_iter > 0) {
-            const uint32_t tm_s[2] = {tmem + TR::TM_S0, tmem + TR::TM_S1};
-            const uint32_t tm_oo[2] = {tmem + TR::TM_O0, tmem + TR::TM_O1};
-            const uint32_t q_addr[2] = {sdesc_lo(smem_u32(sQ), 16), sdesc_lo(smem_u32(sQ + TR::TILE_BYTES), 16)};
+        // The whole warp walks the loop converged and only the MMA / commit instructions are predicated on one elected
+        // lane (a converged warp issues an MMA every ~39 cycles and commits for free; a lone lane in a divergent branch
+        // pays ~44 per MMA and ~44 more per commit).  Waits and commits cost tensor-pipe time (its queue is about one MMA
+        // deep), so there are as few as the hazards allow: per iteration one wait for the K/V group, two per query tile
+        // for the halves of P, one commit per tile (S ready; since a commit covers everything issued before it, it also
+        // tells the softmax that the previous P.V has completed) and one commit that frees the K/V group.
+        if (n_iter > 0) {
+            const bool leader = elect_one_lane();
             const uint32_t k_lo0 = sdesc_lo(smem_u32(sK), 16), v_lo0 = sdesc_lo(smem_u32(sV), TR::PANEL_BYTES);
             constexpr uint32_t kStage = TR::TILE_BYTES >> 4;
             mbar_wait(q_full, 0, ab, 20);
-            mbar_wait(&k_full[0], 0, ab, 21);
             tc_fence_after_sync();
+#pragma unroll
             for (int i = 0; i < 2; ++i)
-                if (n_kv[i] > 0) { fwd_issue_s<TR>(tm_s[i], q_addr[i], k_lo0); umma_commit(&s_full[i]); }
-            umma_commit(&k_empty[0]);
+                if (n_kv[i] > 0) {
+                    fwd_issue_s<TR>(tmem + (i ? TR::TM_S1 : TR::TM_S0), sdesc_lo(smem_u32(sQ + i * TR::TILE_BYTES), 16), k_lo0, leader);
+                    if (leader) umma_commit(&s_full[i]);
+                }
+            if (leader) umma_commit(k0_free);
             for (int j = 0; j < n_iter; ++j) {
                 const int sv = j % KS;
-                const int sk_next = (j + 1) % KS;
-                const bool has_next = (j + 1) < n_iter;
-                if (has_next) mbar_wait(&k_full[sk_next], ((j + 1) / KS) & 1, ab, 22);
-                mbar_wait(&v_full[sv], (j / KS) & 1, ab, 23);
+                const uint32_t v_lo = v_lo0 + sv * kStage, k_next_lo = k_lo0 + ((j + 1) % KS) * kStage;
+                mbar_wait(&kv_full[sv], (j / KS) & 1, ab, 22);
+#pragma unroll
                 for (int i = 0; i < 2; ++i) {
                     if (j < n_kv[i]) {
+                        const uint32_t tm_s = tmem + (i ? TR::TM_S1 : TR::TM_S0), tm_o = tmem + (i ? TR::TM_O1 : TR::TM_O0);
                         // P arrives in two halves of 64 key columns: the first k-steps of P.V run under the second half's exponentials
                         mbar_wait(&p_half[2 * i], j & 1, ab, 24);
                         tc_fence_after_sync();
                         if constexpr (!TR::SPLIT) {
-                            fwd_issue_pv_part<TR, 0, TR::PV_KSTEPS / 2>(tm_oo[i], tm_s[i], v_lo0 + sv * kStage, j == 0);
+                            fwd_issue_pv_part<TR, 0, TR::PV_KSTEPS / 2>(tm_o, tm_s, v_lo, j == 0, leader);
                             mbar_wait(&p_half[2 * i + 1], j & 1, ab, 25);
                             tc_fence_after_sync();
-                            fwd_issue_pv_part<TR, TR::PV_KSTEPS / 2, TR::PV_KSTEPS>(tm_oo[i], tm_s[i], v_lo0 + sv * kStage, j == 0);
+                            fwd_issue_pv_part<TR, TR::PV_KSTEPS / 2, TR::PV_KSTEPS>(tm_o, tm_s, v_lo, j == 0, leader);
                         } else {
                             mbar_wait(&p_half[2 * i + 1], j & 1, ab, 25);
                             tc_fence_after_sync();
-                            fwd_issue_pv<TR>(tm_oo[i], tm_s[i], v_lo0 + sv * kStage, j == 0);
+                            fwd_issue_pv<TR>(tm_o, tm_s, v_lo, j == 0, leader);
                         }
-                        umma_commit(&o_full[i]);
                         if (j + 1 < n_kv[i]) {
-                            fwd_issue_s<TR>(tm_s[i], q_addr[i], k_lo0 + sk_next * kStage);
-                            umma_commit(&s_full[i]);
+                            fwd_issue_s<TR>(tm_s, sdesc_lo(smem_u32(sQ + i * TR::TILE_BYTES), 16), k_next_lo, leader);
+                            if (leader) umma_commit(&s_full[i]);
+                        } else {
+                            if (leader) umma_commit(&o_full[i]);           // last key tile of this query tile: O_i is final
                         }
                     }
                 }
-                umma_commit(&v_empty[sv]);
-                if (has_next) umma_commit(&k_empty[sk_next]);
+                if (leader) umma_commit(&kv_empty[sv]);
             }
         }
     } else if (warp < 8) {
@@ -293,8 +306,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             } else {
                 const bool need = mx_s > m_used + kRescaleLog2;
                 if (__any_sync(0xffffffffu, need)) {
-                    mbar_wait(&o_full[i], (j - 1) & 1, ab, 31);
-                    tc_fence_after_sync();
+                    // P.V_{j-1} has completed: this iteration's S commit was issued after it
                     const float alpha = need ? fast_exp2(m_used - mx_s) : 1.f;
                     if (need) { m_used = mx_s; l *= alpha; }
 #pragma unroll
@@ -350,7 +362,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
 
         if (nkv > 0) {
-            mbar_wait(&o_full[i], (nkv - 1) & 1, ab, 32);
+            mbar_wait(&o_full[i], 0, ab, 32);
             tc_fence_after_sync();
             const float inv_l = 1.f / l;
             uint8_t* stage = sQ + i * TR::TILE_BYTES;     // Q_i is dead once its last S MMA has completed
