@@ -103,36 +103,36 @@ __device__ __forceinline__ uint32_t bwd_pcol(int ks, int part = 0) { return stat
 
 // acc[128 keys x 64 queries] = A B^T with A = K or V tile, B = Q or dO block, both K-major (S^T and dP^T).
 template <class TR>
-__device__ __forceinline__ void bwd_issue_kmajor(uint32_t tmem_acc, uint32_t a_lo, uint32_t b_lo) {
+__device__ __forceinline__ void bwd_issue_kmajor(uint32_t tmem_acc, uint32_t a_lo, uint32_t b_lo, bool leader) {
     if constexpr (!TR::SPLIT) {
 #pragma unroll
         for (int k = 0; k < TR::D / 16; ++k)
-            umma_ss_f16(tmem_acc, sdesc_join(a_lo + (((k / 4) * TR::KV_PANEL + (k % 4) * 32) >> 4)),
+            if (leader) umma_ss_f16(tmem_acc, sdesc_join(a_lo + (((k / 4) * TR::KV_PANEL + (k % 4) * 32) >> 4)),
                         sdesc_join(b_lo + (((k / 4) * TR::Q_PANEL + (k % 4) * 32) >> 4)), TR::IDESC_ST, k > 0);
     } else {
 #pragma unroll
         for (int t = 0; t < 3; ++t)
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-                umma_ss_f16(tmem_acc, sdesc_join(a_lo + ((split_a(t) * TR::KV_PANEL + k * 32) >> 4)),
+                if (leader) umma_ss_f16(tmem_acc, sdesc_join(a_lo + ((split_a(t) * TR::KV_PANEL + k * 32) >> 4)),
                             sdesc_join(b_lo + ((split_b(t) * TR::Q_PANEL + k * 32) >> 4)), TR::IDESC_ST, (t | k) != 0);
     }
 }
 
 // acc[128 keys x D] += A B with A = P^T or dS^T in TMEM (64 queries), B = dO or Q block, MN-major (dV and dK).
 template <class TR>
-__device__ __forceinline__ void bwd_issue_acc(uint32_t tmem_acc, uint32_t tmem_a, int part, uint32_t b_lo_mn, bool accumulate) {
+__device__ __forceinline__ void bwd_issue_acc(uint32_t tmem_acc, uint32_t tmem_a, int part, uint32_t b_lo_mn, bool accumulate, bool leader) {
     if constexpr (!TR::SPLIT) {
 #pragma unroll
         for (int ks = 0; ks < TR::BQ / 16; ++ks)
-            umma_ts_f16(tmem_acc, tmem_a + bwd_pcol(ks, part), sdesc_join(b_lo_mn + ((ks * 2048) >> 4)), TR::IDESC_DKV,
+            if (leader) umma_ts_f16(tmem_acc, tmem_a + bwd_pcol(ks, part), sdesc_join(b_lo_mn + ((ks * 2048) >> 4)), TR::IDESC_DKV,
                         (accumulate || ks > 0) ? 1u : 0u);
     } else {
 #pragma unroll
         for (int t = 0; t < 3; ++t)
 #pragma unroll
             for (int ks = 0; ks < TR::BQ / 16; ++ks)
-                umma_ts_f16(tmem_acc, tmem_a + bwd_pcol(ks, split_a(t)),
+                if (leader) umma_ts_f16(tmem_acc, tmem_a + bwd_pcol(ks, split_a(t)),
                             sdesc_join(b_lo_mn + ((split_b(t) * TR::Q_PANEL + ks * 2048) >> 4)), TR::IDESC_DKV,
                             (accumulate || (t | ks) != 0) ? 1u : 0u);
     }
@@ -140,17 +140,17 @@ __device__ __forceinline__ void bwd_issue_acc(uint32_t tmem_acc, uint32_t tmem_a
 
 // acc[D x 64 queries] = K^T dS^T with K MN-major (M = head dim) and dS^T MN-major (N = queries).
 template <class TR>
-__device__ __forceinline__ void bwd_issue_dq(uint32_t tmem_acc, uint32_t k_lo_mn, uint32_t ds_lo) {
+__device__ __forceinline__ void bwd_issue_dq(uint32_t tmem_acc, uint32_t k_lo_mn, uint32_t ds_lo, bool leader) {
     if constexpr (!TR::SPLIT) {
 #pragma unroll
         for (int ks = 0; ks < TR::BKV / 16; ++ks)
-            umma_ss_f16(tmem_acc, sdesc_join(k_lo_mn + ((ks * 2048) >> 4)), sdesc_join(ds_lo + ((ks * 2048) >> 4)), TR::IDESC_DQ, ks > 0);
+            if (leader) umma_ss_f16(tmem_acc, sdesc_join(k_lo_mn + ((ks * 2048) >> 4)), sdesc_join(ds_lo + ((ks * 2048) >> 4)), TR::IDESC_DQ, ks > 0);
     } else {
 #pragma unroll
         for (int t = 0; t < 3; ++t)
 #pragma unroll
             for (int ks = 0; ks < TR::BKV / 16; ++ks)
-                umma_ss_f16(tmem_acc, sdesc_join(k_lo_mn + ((split_a(t) * TR::KV_PANEL + ks * 2048) >> 4)),
+                if (leader) umma_ss_f16(tmem_acc, sdesc_join(k_lo_mn + ((split_a(t) * TR::KV_PANEL + ks * 2048) >> 4)),
                             sdesc_join(ds_lo + ((split_b(t) * TR::DS_PART + ks * 2048) >> 4)), TR::IDESC_DQ, (t | ks) != 0);
     }
 }
@@ -253,7 +253,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
     } else if (warp == 13) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
+        // The whole warp walks the loop converged; only the MMA and commit instructions are predicated on one elected lane
+        // (a converged warp issues an MMA every ~39 cycles and commits for free; a lone lane in a divergent branch pays
+        // ~44 per MMA and ~44 more per commit).
+        {
+            const bool leader = elect_one_lane();
             // descriptor low words: K-major views (lbo unused = 16) and MN-major views (lbo = panel stride)
             const uint32_t lK = sdesc_lo(smem_u32(sK), 16), lV = sdesc_lo(smem_u32(sV), 16);
             const uint32_t lK_mn = sdesc_lo(smem_u32(sK), TR::KV_PANEL), lDS = sdesc_lo(smem_u32(sDS), 16);
@@ -266,10 +270,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const int b = blk & 1, s = blk % NS;
                 mbar_wait(&qdo_full[s], (blk / NS) & 1, ab, 21);
                 tc_fence_after_sync();
-                bwd_issue_kmajor<TR>(tmem + TR::TM_ST + b * 64, lK, lQ0 + s * kStage);
+                bwd_issue_kmajor<TR>(tmem + TR::TM_ST + b * 64, lK, lQ0 + s * kStage, leader);
                 if (blk >= 2) { mbar_wait(&dq_empty[b], ((blk - 2) >> 1) & 1, ab, 24); tc_fence_after_sync(); }
-                bwd_issue_kmajor<TR>(tmem + TR::TM_DP + b * 64, lV, lDO0 + s * kStage);
-                umma_commit(&sdp_full[b]);
+                bwd_issue_kmajor<TR>(tmem + TR::TM_DP + b * 64, lV, lDO0 + s * kStage, leader);
+                if (leader) umma_commit(&sdp_full[b]);
             };
             issue_front(0);
             if (nblk > 1) issue_front(1);
@@ -280,20 +284,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 mbar_wait(&pds_full[b], (it >> 1) & 1, ab, 22);
                 tc_fence_after_sync();
                 if constexpr (!TR::SPLIT) {
-                    bwd_issue_dq<TR>(t_dp, lK_mn, lDS);                            // dQ^T(it) over the consumed dP^T buffer
-                    umma_commit(&dq_full[b]);
-                    bwd_issue_acc<TR>(tmem + TR::TM_DK, t_st, 1, lQ_mn, it > 0);   // dK += dS^T Q
-                    bwd_issue_acc<TR>(tmem + TR::TM_DV, t_st, 0, lDO_mn, it > 0);  // dV += P^T dO
+                    bwd_issue_dq<TR>(t_dp, lK_mn, lDS, leader);                            // dQ^T(it) over the consumed dP^T buffer
+                    if (leader) umma_commit(&dq_full[b]);
+                    bwd_issue_acc<TR>(tmem + TR::TM_DK, t_st, 1, lQ_mn, it > 0, leader);   // dK += dS^T Q
+                    bwd_issue_acc<TR>(tmem + TR::TM_DV, t_st, 0, lDO_mn, it > 0, leader);  // dV += P^T dO
                 } else {
-                    bwd_issue_acc<TR>(tmem + TR::TM_DV, t_st, 0, lDO_mn, it > 0);
-                    bwd_issue_acc<TR>(tmem + TR::TM_DK, t_dp, 0, lQ_mn, it > 0);
-                    bwd_issue_dq<TR>(t_dp, lK_mn, lDS);
-                    umma_commit(&dq_full[b]);
+                    bwd_issue_acc<TR>(tmem + TR::TM_DV, t_st, 0, lDO_mn, it > 0, leader);
+                    bwd_issue_acc<TR>(tmem + TR::TM_DK, t_dp, 0, lQ_mn, it > 0, leader);
+                    bwd_issue_dq<TR>(t_dp, lK_mn, lDS, leader);
+                    if (leader) umma_commit(&dq_full[b]);
                 }
-                umma_commit(&qdo_empty[s]);
+                if (leader) umma_commit(&qdo_empty[s]);
                 if (it + 2 < nblk) issue_front(it + 2);
             }
-            umma_commit(dkv_full);
+            if (leader) umma_commit(dkv_full);
         }
     } else if (warp < 8) {
         // ------------------------------ compute: P^T and dS^T ------------------------------
