@@ -35,7 +35,7 @@
 //                thread owns one key row; warps 0-3 take query columns 0-31, 4-7 take 32-63
 //   warps 8-11   drain dQ^T from TMEM to the global accumulator
 //   warp 12      TMA producer (K, V once; Q, dO, lse, delta per query block)
-//   warp 13      MMA issuer (one lane)
+//   warp 13      MMA issuer (converged warp, one elected lane issues)
 #pragma once
 
 #include "attn_aux.cuh"

@@ -10,16 +10,19 @@
 // One CTA owns two adjacent 128-row query tiles of one (batch, head) and walks the
 // key/value tiles up to the diagonal:
 //   warps 10-11 idle (they only donate registers)
-//   warp 9      TMA producer: Q tiles once, then K_j / V_j into two rings
-//   warp 8      MMA issuer (one lane): S_i = Q_i K_j^T (smem x smem -> TMEM) and
-//               O_i += P_i V_j (P read from TMEM, V from smem, MN-major)
+//   warp 9      TMA producer: the Q tiles and K_0 once, then one load group {K_{j+1}, V_j}
+//               per iteration (exactly what iteration j of the MMA warp consumes)
+//   warp 8      MMA issuer: the warp stays converged and one elected lane issues
+//               S_i = Q_i K_j^T (smem x smem -> TMEM) and O_i += P_i V_j (P read from
+//               TMEM, V from smem, MN-major)
 //   warps 0-3   softmax for query tile 0 (one thread per row, no shuffles needed:
 //               the 32x32b TMEM load gives each thread a whole row)
 //   warps 4-7   softmax for query tile 1
 // While one softmax group exponentiates, the tensor core works for the other.
-// P overwrites S in place in TMEM.  O stays in TMEM for the whole walk; it is
-// rescaled only when a row maximum grows by more than 2^kRescaleLog2 ("lazy"
-// rescale), which the final division by the row sum makes exact.
+// P overwrites S in place in TMEM and is published to the MMA warp in two halves of 64
+// keys.  O stays in TMEM for the whole walk; it is rescaled only when a row maximum
+// grows by more than 2^kRescaleLog2 ("lazy" rescale), which the final division by the
+// row sum makes exact.
 #pragma once
 
 #include "sm100_ptx.cuh"

@@ -122,7 +122,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
+        // The warp stays converged; only the MMA / commit instructions are predicated on one elected lane (commits are
+        // then free, where a lone lane in a divergent branch pays ~44 cycles of tensor-pipe time for each).
+        {
+            const bool leader = elect_one_lane();
             constexpr uint32_t idesc = make_idesc(kFmtBF16, BM, BN, A_MN ? kMajorMN : kMajorK, B_MN ? kMajorMN : kMajorK);
             int it = 0, tcount = 0;
             for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++tcount) {
@@ -140,11 +143,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     for (int k = 0; k < BK / 16; ++k) {
                         const uint32_t ao = A_MN ? (k * 2048) >> 4 : (k * 32) >> 4;
                         const uint32_t bo = B_MN ? (k * 2048) >> 4 : (k * 32) >> 4;
-                        umma_ss_f16(tmem + buf * BN, sdesc_join(a_lo + ao), sdesc_join(b_lo + bo), idesc, ((ks - ks0) | k) != 0);
+                        if (leader) umma_ss_f16(tmem + buf * BN, sdesc_join(a_lo + ao), sdesc_join(b_lo + bo), idesc, ((ks - ks0) | k) != 0);
                     }
-                    umma_commit(&empty[s]);
+                    if (leader) umma_commit(&empty[s]);
                 }
-                umma_commit(&acc_full[buf]);
+                if (leader) umma_commit(&acc_full[buf]);
             }
         }
     } else {
