@@ -13,7 +13,9 @@ def rel(a, b):
     return float((a.float() - b.float()).norm() / b.float().norm())
 
 
-@pytest.mark.parametrize("M,K,N", [(128, 64, 256), (256, 768, 2304), (1000, 768, 768), (136, 72, 264), (4096, 3072, 768)])
+@pytest.mark.parametrize("M,K,N", [(128, 64, 256), (256, 768, 2304), (1000, 768, 768), (136, 72, 264), (4096, 3072, 768),
+                                   (8192, 256, 256),     # weight gradient: 2 output tiles, split-K over 8 slabs
+                                   (128, 8192, 256)])    # forward: 1 output tile, split-K with the bias going in once
 def test_forward_and_backward_match_float32_reference(M, K, N):
     g = torch.Generator(device="cuda").manual_seed(M + K + N)
     x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
