@@ -13,11 +13,20 @@ namespace ib200 {
 
 // ----------------------------------------------------------------------------
 // Bounded waits.  No wait in this library spins forever: after kSpinLimit failed
-// polls the waiter raises the CTA-wide abort flag and records a code in the
-// kernel's global status word; every later wait in that CTA returns at once, the
-// CTA runs to its normal tear-down (TMEM freed) and the host reports an error.
+// polls, or kWaitLimitNs of wall-clock time (a failed try_wait may itself suspend the
+// thread for a system-dependent while, so a poll count alone does not bound time),
+// the waiter raises the CTA-wide abort flag and records a code in the kernel's global
+// status word; every later wait in that CTA returns at once, the CTA runs to its
+// normal tear-down (TMEM freed) and the host reports an error.
 // ----------------------------------------------------------------------------
 constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr unsigned long long kWaitLimitNs = 4000000000ull;      // 4 s: three orders of magnitude above the longest kernel
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 enum : int {
     kDevOk = 0,
@@ -77,11 +86,14 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ab, int site) {
     if (mbar_test_wait(bar, parity)) return true;
     uint32_t spins = 0;
+    unsigned long long t_start = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 63u) == 0) {
             if (*ab.cta_flag != 0) return false;
-            if (spins > kSpinLimit) {
+            const unsigned long long now = global_timer_ns();
+            if (t_start == 0) t_start = now;
+            if (spins > kSpinLimit || now - t_start > kWaitLimitNs) {
                 *ab.cta_flag = 1;
                 if (ab.status) atomicCAS(ab.status, 0, kDevTimeoutBase + site);
                 return false;
