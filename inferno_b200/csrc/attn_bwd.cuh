@@ -428,7 +428,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 for (int p = 0; p < TR::OUT_PANELS; ++p)
                     tma_store_4d(h ? &tm_dk : &tm_dv, stage + p * TR::KV_PANEL, p * TR::OUT_PANEL_ELEMS, n * BKV, hd, bt);
                 tma_store_commit();
-                tma_store_wait_all();
+                tma_store_wait_read_all();     // the CTA may leave once its shared memory has been read; the writes complete on their own
             }
         }
     } else if (warp < 12) {
@@ -467,7 +467,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 tma_store_commit();
             }
         }
-        if (issuer) tma_store_wait_all();
+        if (issuer) tma_store_wait_read_all();     // the CTA may leave once its shared memory has been read; the writes complete on their own
     }
 
     // ------------------------------ tear-down ------------------------------

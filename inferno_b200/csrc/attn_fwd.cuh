@@ -407,7 +407,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 for (int p = 0; p < TR::OUT_PANELS; ++p)
                     tma_store_4d(&tm_o, stage + p * TR::PANEL_BYTES, p * TR::OUT_PANEL_ELEMS, m_tile[i] * BM, hd, bt);
                 tma_store_commit();
-                tma_store_wait_all();
+                tma_store_wait_read_all();     // the CTA may leave once its shared memory has been read; the writes complete on their own
             }
         }
     }

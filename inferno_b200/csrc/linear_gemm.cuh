@@ -203,7 +203,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 }
             }
         }
-        if (tid == 0) tma_store_wait_all();
+        if (tid == 0) tma_store_wait_read_all();     // the CTA may leave once its shared memory has been read; the writes complete on their own
     }
 
     tc_fence_before_sync();
