@@ -78,3 +78,42 @@ class Linear(torch.nn.Module):
 
     def forward(self, x):
         return LinearFunction.apply(x, self.weight, self.bias)
+
+
+def _time_shape(M: int, K: int, N: int, iters: int = 20):
+    """Forward and backward of one projection on synthetic bf16 data, timed with CUDA events."""
+    g = torch.Generator(device="cuda").manual_seed(M + K + N)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(K, N, device="cuda", generator=g) / K ** 0.5).to(torch.bfloat16)
+    b = torch.randn(N, device="cuda", generator=g)
+    dy = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    fwd = timed(lambda: linear_forward(x, w, b))
+    bwd = timed(lambda: linear_backward(x, w, dy))
+    flop = 2.0 * M * K * N
+    return dict(M=M, K=K, N=N, fwd_ms=fwd, fwd_tflops=flop / fwd / 1e9, bwd_ms=bwd, bwd_tflops=2 * flop / bwd / 1e9)
+
+
+if __name__ == "__main__":
+    import argparse
+    import json
+
+    ap = argparse.ArgumentParser(description="time y = x W + b and its backward (dX, dW, db) on one GPU")
+    ap.add_argument("M", type=int, nargs="?", default=16384)
+    ap.add_argument("K", type=int, nargs="?", default=768)
+    ap.add_argument("N", type=int, nargs="?", default=2304)
+    ap.add_argument("--iters", type=int, default=20)
+    a = ap.parse_args()
+    print(json.dumps(_time_shape(a.M, a.K, a.N, a.iters)))
