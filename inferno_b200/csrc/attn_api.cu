@@ -235,7 +235,7 @@ int launch_bwd_all(const void* q, const void* k, const void* v, const void* o, c
         rc = launch_bwd<BwdTraits<64, true>>(&part[0], &part[2], &part[4], &part[6], dl, dl, dl, dl, L.dk, L.dv, nlse2, ndelta, T_pad,
                                              dq_acc, dk, dv, status, BH, T, scale, causal, stream);
         if (rc) return rc;
-        return launch_dq_finish<true>(dq_acc, dq, scale, L.dq, BH, T, D, stream);
+        return launch_dq_finish<64, true>(dq_acc, dq, scale, L.dq, BH, T, stream);
     }
     const void* qq[2] = {q, q}; const void* kk[2] = {k, k}; const void* vv[2] = {v, v}; const void* dd[2] = {dO, dO};
     if (D == 64) {
@@ -248,7 +248,8 @@ int launch_bwd_all(const void* q, const void* k, const void* v, const void* o, c
                                                BH, T, scale, causal, stream);
     }
     if (rc) return rc;
-    return launch_dq_finish<false>(dq_acc, dq, scale, L.dq, BH, T, D, stream);
+    return D == 64 ? launch_dq_finish<64, false>(dq_acc, dq, scale, L.dq, BH, T, stream)
+                   : launch_dq_finish<128, false>(dq_acc, dq, scale, L.dq, BH, T, stream);
 }
 
 // A caller-supplied layout (NULL = dense), checked: rows of D elements must start on 16-byte boundaries.

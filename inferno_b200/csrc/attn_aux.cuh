@@ -9,6 +9,8 @@
 // All are grid-stride, 16-byte vectorised and coalesced; grids are sized from the SM count.
 #pragma once
 
+#include <type_traits>
+
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -94,29 +96,41 @@ __global__ void __launch_bounds__(kAuxThreads) cast_bf16_f32_kernel(const uint4*
 template <int D, bool F32>
 __global__ void __launch_bounds__(kAuxThreads) delta_kernel(const void* __restrict__ o_, const void* __restrict__ do_, const float* __restrict__ lse,
                                                             float* __restrict__ ndelta, float* __restrict__ nlse2, RowLayout lo, RowLayout ldo,
-                                                            long heads, int T, int T_pad) {
+                                                            int T, int T_pad) {
     constexpr int EPT = F32 ? 4 : 8;              // elements per 16-byte load
     constexpr int TPR = D / EPT;                  // threads per row (8 or 16)
     constexpr int RPB = kAuxThreads / TPR;        // rows per block per step
+    constexpr int U = 4;                          // steps per block: 2 * U independent 16-byte loads in flight per thread
+    using Vec = typename std::conditional<F32, float4, uint4>::type;
     const int sub = threadIdx.x % TPR;
-    const long rows_pad = heads * T_pad;
-    const long row0 = blockIdx.x * static_cast<long>(RPB) + threadIdx.x / TPR;
-    for (long prow = row0; prow < rows_pad; prow += static_cast<long>(gridDim.x) * RPB) {
-        const long head = prow / T_pad;
-        const int t = static_cast<int>(prow - head * T_pad);
+    const long head = blockIdx.y;                 // one head per grid row: no per-row divisions
+    const int t0 = blockIdx.x * (RPB * U) + threadIdx.x / TPR;
+    const long base_o = lo.row(head, 0), base_do = ldo.row(head, 0);
+    Vec a[U], b[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int t = t0 + u * RPB;
+        if (t < T) {
+            if constexpr (F32) {
+                a[u] = reinterpret_cast<const float4*>(static_cast<const float*>(o_) + base_o + static_cast<long>(t) * lo.st)[sub];
+                b[u] = reinterpret_cast<const float4*>(static_cast<const float*>(do_) + base_do + static_cast<long>(t) * ldo.st)[sub];
+            } else {
+                a[u] = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(o_) + base_o + static_cast<long>(t) * lo.st)[sub];
+                b[u] = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(do_) + base_do + static_cast<long>(t) * ldo.st)[sub];
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int t = t0 + u * RPB;
         const bool live = t < T;
-        const long row = head * T + t;
         float acc = 0.f;
         if (live) {
             if constexpr (F32) {
-                const float4 a = reinterpret_cast<const float4*>(static_cast<const float*>(o_) + lo.row(head, t))[sub];
-                const float4 b = reinterpret_cast<const float4*>(static_cast<const float*>(do_) + ldo.row(head, t))[sub];
-                acc = a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+                acc = a[u].x * b[u].x + a[u].y * b[u].y + a[u].z * b[u].z + a[u].w * b[u].w;
             } else {
-                const uint4 a = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(o_) + lo.row(head, t))[sub];
-                const uint4 b = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(do_) + ldo.row(head, t))[sub];
-                const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-                const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+                const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a[u]);
+                const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b[u]);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const float2 fa = __bfloat1622float2(pa[e]), fb = __bfloat1622float2(pb[e]);
@@ -125,11 +139,13 @@ __global__ void __launch_bounds__(kAuxThreads) delta_kernel(const void* __restri
                 }
             }
         }
+        // every thread of a row group takes part in the shuffles (t is uniform per group)
 #pragma unroll
         for (int off = TPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-        if (sub == 0) {
+        if (sub == 0 && t < T_pad) {
+            const long prow = head * T_pad + t;
             ndelta[prow] = -acc;
-            nlse2[prow] = live ? lse[row] * -1.4426950408889634f : 0.f;
+            nlse2[prow] = live ? lse[head * T + t] * -1.4426950408889634f : 0.f;
         }
     }
 }
@@ -138,50 +154,60 @@ template <int D, bool F32>
 inline int launch_delta(const void* o, const void* dO, const float* lse, float* ndelta, float* nlse2, const RowLayout& lo,
                         const RowLayout& ldo, long heads, int T, int T_pad, cudaStream_t stream) {
     constexpr int RPB = kAuxThreads / (D / (F32 ? 4 : 8));
-    // every thread of a block takes part in the shuffles: the row loop bound is uniform per TPR group
-    long blocks = (heads * T_pad + RPB - 1) / RPB;
-    if (blocks > kAuxBlocks) blocks = kAuxBlocks;
-    delta_kernel<D, F32><<<static_cast<int>(blocks), kAuxThreads, 0, stream>>>(o, dO, lse, ndelta, nlse2, lo, ldo, heads, T, T_pad);
+    dim3 grid((T_pad + RPB * 4 - 1) / (RPB * 4), static_cast<unsigned>(heads), 1);
+    delta_kernel<D, F32><<<grid, kAuxThreads, 0, stream>>>(o, dO, lse, ndelta, nlse2, lo, ldo, T, T_pad);
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 
 // out[row, :] = scale * acc[row, :], 8 elements per thread; acc is dense [heads, T, D], out follows `lout`.
-template <bool F32>
+// One head per grid row and a power-of-two row length: no divisions in the index arithmetic; U chunks per thread
+// so that 2 * U 16-byte loads are in flight.
+template <int D, bool F32>
 __global__ void __launch_bounds__(kAuxThreads) dq_finish_kernel(const float4* __restrict__ acc, void* __restrict__ out, float scale,
-                                                                RowLayout lout, long heads, int T, int D) {
-    const int cpr = D / 8;
-    const long n8 = heads * T * cpr;
-    for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
-        const long rowi = i / cpr;
-        const int c8 = static_cast<int>(i - rowi * cpr);
-        const long head = rowi / T;
-        const int t = static_cast<int>(rowi - head * T);
-        const long dst = lout.row(head, t) + c8 * 8;
-        float4 a = acc[2 * i], b = acc[2 * i + 1];
-        a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
-        b.x *= scale; b.y *= scale; b.z *= scale; b.w *= scale;
+                                                                RowLayout lout, int T) {
+    constexpr int CPR = D / 8;                    // 8-element chunks per row
+    constexpr int U = 4;
+    const long head = blockIdx.y;
+    const long base_out = lout.row(head, 0);
+    const float4* acc_h = acc + head * static_cast<long>(T) * CPR * 2;
+    const int n8 = T * CPR;                       // chunks of this head
+    const int i0 = blockIdx.x * (kAuxThreads * U) + threadIdx.x;
+    float4 a[U], b[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int i = i0 + u * kAuxThreads;
+        if (i < n8) { a[u] = acc_h[2 * i]; b[u] = acc_h[2 * i + 1]; }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int i = i0 + u * kAuxThreads;
+        if (i >= n8) continue;
+        const int t = i / CPR, c8 = i % CPR;
+        const long dst = base_out + static_cast<long>(t) * lout.st + c8 * 8;
+        float4 x = a[u], y = b[u];
+        x.x *= scale; x.y *= scale; x.z *= scale; x.w *= scale;
+        y.x *= scale; y.y *= scale; y.z *= scale; y.w *= scale;
         if constexpr (F32) {
             float4* o4 = reinterpret_cast<float4*>(static_cast<float*>(out) + dst);
-            o4[0] = a;
-            o4[1] = b;
+            o4[0] = x;
+            o4[1] = y;
         } else {
             uint4 v;
             __nv_bfloat162 t2;
-            t2 = __floats2bfloat162_rn(a.x, a.y); v.x = *reinterpret_cast<uint32_t*>(&t2);
-            t2 = __floats2bfloat162_rn(a.z, a.w); v.y = *reinterpret_cast<uint32_t*>(&t2);
-            t2 = __floats2bfloat162_rn(b.x, b.y); v.z = *reinterpret_cast<uint32_t*>(&t2);
-            t2 = __floats2bfloat162_rn(b.z, b.w); v.w = *reinterpret_cast<uint32_t*>(&t2);
+            t2 = __floats2bfloat162_rn(x.x, x.y); v.x = *reinterpret_cast<uint32_t*>(&t2);
+            t2 = __floats2bfloat162_rn(x.z, x.w); v.y = *reinterpret_cast<uint32_t*>(&t2);
+            t2 = __floats2bfloat162_rn(y.x, y.y); v.z = *reinterpret_cast<uint32_t*>(&t2);
+            t2 = __floats2bfloat162_rn(y.z, y.w); v.w = *reinterpret_cast<uint32_t*>(&t2);
             *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out) + dst) = v;
         }
     }
 }
 
-template <bool F32>
-inline int launch_dq_finish(const float* acc, void* out, float scale, const RowLayout& lout, long heads, int T, int D, cudaStream_t stream) {
-    const long n8 = heads * T * D / 8;
-    long blocks = n8 / kAuxThreads + 1;
-    if (blocks > kAuxBlocks) blocks = kAuxBlocks;
-    dq_finish_kernel<F32><<<static_cast<int>(blocks), kAuxThreads, 0, stream>>>(reinterpret_cast<const float4*>(acc), out, scale, lout, heads, T, D);
+template <int D, bool F32>
+inline int launch_dq_finish(const float* acc, void* out, float scale, const RowLayout& lout, long heads, int T, cudaStream_t stream) {
+    const int n8 = T * (D / 8);
+    dim3 grid((n8 + kAuxThreads * 4 - 1) / (kAuxThreads * 4), static_cast<unsigned>(heads), 1);
+    dq_finish_kernel<D, F32><<<grid, kAuxThreads, 0, stream>>>(reinterpret_cast<const float4*>(acc), out, scale, lout, T);
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 
