@@ -34,15 +34,16 @@ constexpr int kAuxBlocks = 148 * 8;
 // Reads rows through `lin` (any layout) and writes hi / lo dense, so the main kernels always see dense
 // operand copies in fp32-I/O mode.
 __global__ void __launch_bounds__(kAuxThreads) split_bf16_kernel(const float* __restrict__ in, uint4* __restrict__ hi, uint4* __restrict__ lo,
-                                                                 RowLayout lin, long heads, int T, int D) {
+                                                                 RowLayout lin, int T, int D) {
     const int cpr = D / 8;                                   // 8-element chunks per row
-    const long n8 = heads * T * cpr;
-    for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
-        const long rowi = i / cpr;
-        const int c8 = static_cast<int>(i - rowi * cpr);
-        const long head = rowi / T;
-        const int t = static_cast<int>(rowi - head * T);
-        const float4* src = reinterpret_cast<const float4*>(in + lin.row(head, t) + c8 * 8);
+    const long head = blockIdx.y;                            // one head per grid row
+    const long base_in = lin.row(head, 0);
+    const int n8 = T * cpr;
+    uint4* hi_h = hi + head * static_cast<long>(n8);
+    uint4* lo_h = lo + head * static_cast<long>(n8);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += gridDim.x * blockDim.x) {
+        const int t = i / cpr, c8 = i - t * cpr;
+        const float4* src = reinterpret_cast<const float4*>(in + base_in + static_cast<long>(t) * lin.st + c8 * 8);
         const float4 a = src[0], b = src[1];
         const float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
         uint32_t h[4], l[4];
@@ -54,16 +55,17 @@ __global__ void __launch_bounds__(kAuxThreads) split_bf16_kernel(const float* __
             h[e] = *reinterpret_cast<const uint32_t*>(&hh);
             l[e] = *reinterpret_cast<const uint32_t*>(&ll);
         }
-        hi[i] = make_uint4(h[0], h[1], h[2], h[3]);
-        lo[i] = make_uint4(l[0], l[1], l[2], l[3]);
+        hi_h[i] = make_uint4(h[0], h[1], h[2], h[3]);
+        lo_h[i] = make_uint4(l[0], l[1], l[2], l[3]);
     }
 }
 
 inline int launch_split_bf16(const float* in, void* hi, void* lo, const RowLayout& lin, long heads, int T, int D, cudaStream_t stream) {
-    const long n8 = heads * T * D / 8;
-    long blocks = n8 / kAuxThreads + 1;
-    if (blocks > kAuxBlocks) blocks = kAuxBlocks;
-    split_bf16_kernel<<<static_cast<int>(blocks), kAuxThreads, 0, stream>>>(in, reinterpret_cast<uint4*>(hi), reinterpret_cast<uint4*>(lo), lin, heads, T, D);
+    const int n8 = T * (D / 8);
+    int bx = (n8 + kAuxThreads - 1) / kAuxThreads;
+    if (bx > 64) bx = 64;                                    // grid-stride inside a head beyond that
+    dim3 grid(bx, static_cast<unsigned>(heads), 1);
+    split_bf16_kernel<<<grid, kAuxThreads, 0, stream>>>(in, reinterpret_cast<uint4*>(hi), reinterpret_cast<uint4*>(lo), lin, T, D);
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 
