@@ -9,6 +9,7 @@
 #include "attn_aux.cuh"
 #include "attn_bwd.cuh"
 #include "attn_fwd.cuh"
+#include "attn_fwd_persist.cuh"
 #include "linear_gemm.cuh"
 
 namespace {
@@ -145,6 +146,40 @@ int launch_fwd(const void* q, const void* q_lo, const void* k, const void* k_lo,
     dim3 grid(pairs, static_cast<unsigned>(BH), 1);
     record_timing_event(0, stream);
     attn_fwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tql, tk, tkl, tv, tvl, to, prm);
+    const bool launched = cuda_ok(cudaGetLastError());
+    record_timing_event(1, stream);
+    return launched ? IB200_OK : IB200_ERR_CUDA;
+}
+
+// bf16 operands: persistent CTAs walking (head, query-tile pair) items, heaviest first.
+template <int D>
+int launch_fwd_persist(const void* q, const void* k, const void* v, void* o, const RowLayout& lq, const RowLayout& lk, const RowLayout& lv,
+                       const RowLayout& lo, float* lse, int* status, long BH, int T, float scale, int causal, cudaStream_t stream) {
+    using TR = FwdPersistTraits<D>;
+    CUtensorMap tq, tk, tv, to;
+    if (!make_tmap(&tq, q, false, D, T, lq, BH, 128) || !make_tmap(&tk, k, false, D, T, lk, BH, 128) ||
+        !make_tmap(&tv, v, false, D, T, lv, BH, 128) || !make_tmap(&to, o, false, D, T, lo, BH, 128))
+        return IB200_ERR_CUDA;
+    if (!cuda_ok(cudaFuncSetAttribute(attn_fwd_persist_kernel<TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::SMEM_BYTES)))
+        return IB200_ERR_CUDA;
+    if (BH > 65535) return IB200_ERR_UNSUPPORTED;
+    FwdPersistParams pp;
+    pp.p.lse = lse;
+    pp.p.status = status;
+    pp.p.T = T;
+    pp.p.BH = static_cast<int>(BH);
+    pp.p.H = lq.H;
+    pp.p.causal = causal;
+    pp.p.scale_log2 = scale * 1.4426950408889634f;
+    pp.pairs_per_head = (T + 255) / 256;
+    const long items = static_cast<long>(pp.pairs_per_head) * BH;
+    if (items > 0x7fffffffL) return IB200_ERR_UNSUPPORTED;
+    pp.n_items = static_cast<int>(items);
+    int dev = 0, sms = 148;
+    if (cuda_ok(cudaGetDevice(&dev))) (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = static_cast<int>(items < sms ? items : sms);
+    record_timing_event(0, stream);
+    attn_fwd_persist_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tk, tv, to, pp);
     const bool launched = cuda_ok(cudaGetLastError());
     record_timing_event(1, stream);
     return launched ? IB200_OK : IB200_ERR_CUDA;
@@ -369,8 +404,8 @@ int fwd_core(const void* q, const void* k, const void* v, void* o, float* lse, c
         return launch_fwd<FwdTraits<64, true>>(part[0], part[1], part[2], part[3], part[4], part[5], o, dl, dl, dl, lo, lse, status, BH, T,
                                                scale, causal, stream);
     }
-    if (D == 64) return launch_fwd<FwdTraits<64, false>>(q, q, k, k, v, v, o, lq, lk, lv, lo, lse, status, BH, T, scale, causal, stream);
-    return launch_fwd<FwdTraits<128, false>>(q, q, k, k, v, v, o, lq, lk, lv, lo, lse, status, BH, T, scale, causal, stream);
+    if (D == 64) return launch_fwd_persist<64>(q, k, v, o, lq, lk, lv, lo, lse, status, BH, T, scale, causal, stream);
+    return launch_fwd_persist<128>(q, k, v, o, lq, lk, lv, lo, lse, status, BH, T, scale, causal, stream);
 }
 
 int bwd_core(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse, void* dq, void* dk, void* dv,
