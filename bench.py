@@ -341,8 +341,8 @@ def finish(args, cfg, world, n, T, D, K, value, ms_step, fwd_ms_max, bwd_ms_max,
         clocks=clocks,
         e2e=e2e,
         gpu_launches=4 * K,
-        kernels_per_step=["attn_fwd_persist_kernel", "delta_kernel", "attn_bwd_kernel", "dq_finish_kernel"],
-        roofline=dict(bound="tensor", kernel=f"attn_bwd_kernel<D={D}>", achieved=achieved, peak=pk["bf16_sustained"],
+        kernels_per_step=["attn_fwd_persist_kernel", "delta_kernel", "attn_bwd_persist_kernel", "dq_finish_kernel"],
+        roofline=dict(bound="tensor", kernel=f"attn_bwd_persist_kernel<D={D}>", achieved=achieved, peak=pk["bf16_sustained"],
                       unit="TFLOP/s", frac=achieved / pk["bf16_sustained"], of=pk["source"],
                       algorithmic_flops_per_launch=bwd_flops_rank, traffic=TRAFFIC_BYTES_PER_ELEMENT * n * T * D if TRAFFIC_BYTES_PER_ELEMENT else None,
                       traffic_source="ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on c3 "

@@ -8,6 +8,7 @@
 
 #include "attn_aux.cuh"
 #include "attn_bwd.cuh"
+#include "attn_bwd_persist.cuh"
 #include "attn_fwd.cuh"
 #include "attn_fwd_persist.cuh"
 #include "linear_gemm.cuh"
@@ -151,6 +152,21 @@ int launch_fwd(const void* q, const void* q_lo, const void* k, const void* k_lo,
     return launched ? IB200_OK : IB200_ERR_CUDA;
 }
 
+// Number of head groups of a persistent kernel's item list (see locate_item).  The CTAs draw items in list order, so at
+// any time they work on a window of about one round (one item per CTA) of the list.  With every head in one group the window
+// would span up to one head per CTA, and the tiles the CTAs of a head share (K / V in the forward; Q / dO and the dQ
+// accumulator in the backward: `shared_bytes_per_head`) would fall out of L2.  So a group is as many heads as keep those
+// tiles within 48 MB, but never fewer than two rounds of items: a group starts with its heaviest items, and it is the
+// second round's light items that let the drawing even out the CTAs before the list ends.
+int persist_head_groups(int ctas, int items_per_head, long BH, size_t shared_bytes_per_head) {
+    const long items = static_cast<long>(items_per_head) * BH;
+    long g = static_cast<long>((48u << 20) / (shared_bytes_per_head ? shared_bytes_per_head : 1));
+    if (g < 1) g = 1;
+    long n_groups = (BH + g - 1) / g;
+    if (n_groups > items / (2L * ctas)) n_groups = items / (2L * ctas);
+    return static_cast<int>(n_groups < 1 ? 1 : n_groups);
+}
+
 // bf16 operands: persistent CTAs walking (head, query-tile pair) items, heaviest first.
 template <int D>
 int launch_fwd_persist(const void* q, const void* k, const void* v, void* o, const RowLayout& lq, const RowLayout& lk, const RowLayout& lv,
@@ -178,6 +194,8 @@ int launch_fwd_persist(const void* q, const void* k, const void* v, void* o, con
     int dev = 0, sms = 148;
     if (cuda_ok(cudaGetDevice(&dev))) (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = static_cast<int>(items < sms ? items : sms);
+    pp.n_groups = persist_head_groups(sms, pp.pairs_per_head, BH, static_cast<size_t>(T) * D * 4 /*K, V*/);
+    pp.next_item = status + 1;              // second word of the workspace header, zeroed with it before every launch
     record_timing_event(0, stream);
     attn_fwd_persist_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tk, tv, to, pp);
     const bool launched = cuda_ok(cudaGetLastError());
@@ -234,6 +252,56 @@ int launch_bwd(const void* const q[2], const void* const k[2], const void* const
     return launched ? IB200_OK : IB200_ERR_CUDA;
 }
 
+// bf16 operands: persistent CTAs walking (head, key tile) items, longest walks first.
+template <class TR>
+int launch_bwd_persist(const void* q, const void* k, const void* v, const void* dO, const RowLayout& lq, const RowLayout& lk, const RowLayout& lv,
+                       const RowLayout& ldo, const RowLayout& ldk, const RowLayout& ldv, const float* nlse2, const float* ndelta, int T_pad,
+                       float* dq_acc, void* dk, void* dv, int* status, long BH, int T, float scale, int causal, cudaStream_t stream) {
+    CUtensorMap tq, tk, tv, tdo, tdk, tdv, tdq;
+    if (!make_tmap(&tq, q, false, TR::D, T, lq, BH, TR::BQ) || !make_tmap(&tdo, dO, false, TR::D, T, ldo, BH, TR::BQ) ||
+        !make_tmap(&tk, k, false, TR::D, T, lk, BH, TR::BKV) || !make_tmap(&tv, v, false, TR::D, T, lv, BH, TR::BKV) ||
+        !make_tmap(&tdk, dk, false, TR::D, T, ldk, BH, TR::BKV) || !make_tmap(&tdv, dv, false, TR::D, T, ldv, BH, TR::BKV))
+        return IB200_ERR_CUDA;
+    {
+        // fp32 dQ accumulator, whole rows of D floats per box row, no swizzle (the staging tile is plain row-major)
+        EncodeTiledFn enc = encode_fn();
+        if (!enc) return IB200_ERR_CUDA;
+        cuuint64_t dims[3] = {static_cast<cuuint64_t>(TR::D), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(BH)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(TR::D) * 4, static_cast<cuuint64_t>(T) * TR::D * 4};
+        cuuint32_t box[3] = {static_cast<cuuint32_t>(TR::D), static_cast<cuuint32_t>(TR::BQ), 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        if (enc(&tdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, dq_acc, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return IB200_ERR_CUDA;
+    }
+    if (!cuda_ok(cudaFuncSetAttribute(attn_bwd_persist_kernel<TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::SMEM_BYTES)))
+        return IB200_ERR_CUDA;
+    if (BH > 65535) return IB200_ERR_UNSUPPORTED;
+    BwdParams prm;
+    prm.nlse2 = nlse2;
+    prm.ndelta = ndelta;
+    prm.T_pad = T_pad;
+    prm.status = status;
+    prm.T = T;
+    prm.BH = static_cast<int>(BH);
+    prm.H = lq.H;
+    prm.causal = causal;
+    prm.scale = scale;
+    prm.scale_log2 = scale * 1.4426950408889634f;
+    const long items = static_cast<long>((T + TR::BKV - 1) / TR::BKV) * BH;
+    if (items > 0x7fffffffL) return IB200_ERR_UNSUPPORTED;
+    int dev = 0, sms = 148;
+    if (cuda_ok(cudaGetDevice(&dev))) (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = static_cast<int>(items < sms ? items : sms);
+    const int n_groups = persist_head_groups(sms, (T + TR::BKV - 1) / TR::BKV, BH, static_cast<size_t>(T) * TR::D * 8 /*Q, dO, fp32 dQ*/);
+    record_timing_event(2, stream);
+    attn_bwd_persist_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdk, tdv, tdq, prm, static_cast<int>(items), n_groups,
+                                                                               status + 1 /*draw counter: header word zeroed before every launch*/);
+    const bool launched = cuda_ok(cudaGetLastError());
+    record_timing_event(3, stream);
+    return launched ? IB200_OK : IB200_ERR_CUDA;
+}
+
 struct BwdLayouts {
     RowLayout q, k, v, o, dO, dq, dk, dv;
 };
@@ -272,15 +340,14 @@ int launch_bwd_all(const void* q, const void* k, const void* v, const void* o, c
         if (rc) return rc;
         return launch_dq_finish<64, true>(dq_acc, dq, scale, L.dq, BH, T, stream);
     }
-    const void* qq[2] = {q, q}; const void* kk[2] = {k, k}; const void* vv[2] = {v, v}; const void* dd[2] = {dO, dO};
     if (D == 64) {
         rc = launch_delta<64, false>(o, dO, lse, ndelta, nlse2, L.o, L.dO, BH, T, T_pad, stream); if (rc) return rc;
-        rc = launch_bwd<BwdTraits<64, false>>(qq, kk, vv, dd, L.q, L.k, L.v, L.dO, L.dk, L.dv, nlse2, ndelta, T_pad, dq_acc, dk, dv, status,
-                                              BH, T, scale, causal, stream);
+        rc = launch_bwd_persist<BwdTraits<64, false>>(q, k, v, dO, L.q, L.k, L.v, L.dO, L.dk, L.dv, nlse2, ndelta, T_pad, dq_acc, dk, dv, status,
+                                                      BH, T, scale, causal, stream);
     } else {
         rc = launch_delta<128, false>(o, dO, lse, ndelta, nlse2, L.o, L.dO, BH, T, T_pad, stream); if (rc) return rc;
-        rc = launch_bwd<BwdTraits<128, false>>(qq, kk, vv, dd, L.q, L.k, L.v, L.dO, L.dk, L.dv, nlse2, ndelta, T_pad, dq_acc, dk, dv, status,
-                                               BH, T, scale, causal, stream);
+        rc = launch_bwd_persist<BwdTraits<128, false>>(q, k, v, dO, L.q, L.k, L.v, L.dO, L.dk, L.dv, nlse2, ndelta, T_pad, dq_acc, dk, dv, status,
+                                                       BH, T, scale, causal, stream);
     }
     if (rc) return rc;
     return D == 64 ? launch_dq_finish<64, false>(dq_acc, dq, scale, L.dq, BH, T, stream)

@@ -31,6 +31,8 @@ struct FwdPersistParams {
     FwdParams p;
     int n_items;        // pairs_per_head * BH
     int pairs_per_head; // ceil(T / 256)
+    int n_groups;       // head groups of the item list (see locate_item)
+    int* next_item;     // draw counter in global memory, zero at launch
 };
 
 template <class TR>
@@ -56,8 +58,10 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     uint64_t* o_full = p_half + 4;          // [2]   after the last P.V of tile i of an item
     uint64_t* o_free = o_full + 2;          // [2]   the epilogue has read O_i out of TMEM (4 warps)
     uint64_t* stage_free = o_free + 2;      // [1]   the TMA store has read the staging tile
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stage_free + 1);
+    uint64_t* ring_bars = stage_free + 1;   // [4]   item ring: full[2], empty[2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_bars + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const ItemRing ring{ring_bars, ring_bars + 2, abort_flag + 1};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int T = prm.T;
@@ -69,8 +73,9 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     struct Item { int bh, hd, bt, m0, m1, nkv0, nkv1, n_iter; };
     auto decode = [&](int idx) {
         Item it;
-        const int pair = pp.pairs_per_head - 1 - idx / BH;         // heaviest (longest walk) first
-        it.bh = idx % BH;
+        int rank;
+        locate_item(HeadGroups{BH, pp.n_groups, pp.pairs_per_head}, idx, rank, it.bh);
+        const int pair = pp.pairs_per_head - 1 - rank;            // the last pair walks the most key tiles: first
         it.hd = it.bh % prm.H;
         it.bt = it.bh / prm.H;
         it.m0 = 2 * pair;
@@ -93,6 +98,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             mbar_init(&o_full[i], 1); mbar_init(&o_free[i], 4);
         }
         mbar_init(stage_free, 1);
+        item_ring_init(ring, 9);                 // readers: the MMA warp and the eight softmax warps
         fence_mbar_init();
     }
     if (warp == 8) { tmem_alloc(tmem_slot, TR::TM_COLS); tmem_relinquish(); }
@@ -110,9 +116,11 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         if (lane == 0) {
             uint32_t G = 0;                               // load groups issued so far (= K tiles = V tiles loaded before this item)
             int n = 0;
-            for (int idx = blockIdx.x; idx < pp.n_items; idx += gridDim.x, ++n) {
+            for (int idx = blockIdx.x; idx < pp.n_items; ++n) {
                 if (*abort_flag != 0) break;
                 const Item it = decode(idx);
+                // draw the next item now; the value is needed (and published to the other roles) only after this item's first loads
+                const int drawn = atomicAdd(pp.next_item, 1);
                 if (n > 0) mbar_wait(q_free, (n - 1) & 1, ab, 12);
                 const int q_tiles = (it.nkv1 > 0) ? 2 : 1;
                 mbar_arrive_expect_tx(q_full, (q_tiles + 1) * TR::TILE_BYTES);
@@ -120,6 +128,8 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 if (q_tiles == 2)
                     for (int p = 0; p < TR::NP; ++p) tma_load_4d(sQ + TR::TILE_BYTES + p * TR::PANEL_BYTES, &tm_q, q_full, p * 64, it.m1 * BM, it.hd, it.bt);
                 for (int p = 0; p < TR::NP; ++p) tma_load_4d(sK + (G % KS) * TR::TILE_BYTES + p * TR::PANEL_BYTES, &tm_k, q_full, p * 64, 0, it.hd, it.bt);
+                idx = static_cast<int>(gridDim.x) + drawn;
+                item_ring_publish(ring, n, idx, ab);
                 for (int j = 0; j < it.n_iter; ++j, ++G) {
                     const int s = G % KS;
                     const bool has_k = (j + 1) < it.n_iter;
@@ -144,7 +154,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         uint32_t pc[2] = {0, 0};          // P tiles consumed so far per query tile (phase of p_half)
         uint32_t oc[2] = {0, 0};          // items in which query tile i was valid (phase of o_free)
         int n = 0;
-        for (int idx = blockIdx.x; idx < pp.n_items; idx += gridDim.x, ++n) {
+        for (int idx = blockIdx.x; idx < pp.n_items; idx = item_ring_next(ring, n++, ab, leader)) {
             if (*abort_flag != 0) break;
             const Item it = decode(idx);
             const int nkv[2] = {it.nkv0, it.nkv1};
@@ -202,7 +212,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         uint32_t sc = 0;                         // S tiles consumed so far (phase of s_full)
         uint32_t oc = 0;                         // items in which this query tile was valid (phase of o_full)
         int n = 0;
-        for (int idx = blockIdx.x; idx < pp.n_items; idx += gridDim.x, ++n) {
+        for (int idx = blockIdx.x; idx < pp.n_items; idx = item_ring_next(ring, n++, ab, lane == 0)) {
             if (*abort_flag != 0) break;
             const Item it = decode(idx);
             const int nkv = i ? it.nkv1 : it.nkv0;

@@ -102,6 +102,60 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     }
 }
 
+// ---- work items of a persistent CTA ---------------------------------------------
+// Every CTA starts on item blockIdx.x and then draws items from a counter in global memory (zero at launch), so a CTA
+// that drew light items simply draws more of them.  One thread of the CTA (the TMA producer, which runs furthest ahead)
+// draws; the other roles read what it drew through a two-slot ring in shared memory: slot n & 1 holds the item that
+// follows the CTA's n-th item, full[] (count 1) says it has been written, empty[] (count = reading warps) that every
+// role has read it.  An index >= the item count ends every role's loop.
+struct ItemRing {
+    uint64_t* full;        // [2]
+    uint64_t* empty;       // [2]
+    volatile int* slot;    // [2]
+};
+__device__ __forceinline__ void item_ring_init(const ItemRing& r, uint32_t readers) {
+    for (int s = 0; s < 2; ++s) { mbar_init(&r.full[s], 1); mbar_init(&r.empty[s], readers); }
+}
+// producer thread: the item after this CTA's n-th item is `next`
+__device__ __forceinline__ void item_ring_publish(const ItemRing& r, int n, int next, const AbortCtx& ab) {
+    const int s = n & 1;
+    mbar_wait(&r.empty[s], ((n >> 1) & 1) ^ 1, ab, 14);
+    r.slot[s] = next;
+    mbar_arrive(&r.full[s]);
+}
+// reading role, called by all its (converged) lanes: the item after this CTA's n-th item
+__device__ __forceinline__ int item_ring_next(const ItemRing& r, int n, const AbortCtx& ab, bool arriving_lane) {
+    const int s = n & 1;
+    mbar_wait(&r.full[s], (n >> 1) & 1, ab, 15);
+    const int v = r.slot[s];
+    __syncwarp();
+    if (arriving_lane) mbar_arrive(&r.empty[s]);
+    return v;
+}
+
+// The item list of a persistent attention kernel runs group by group over consecutive heads (so that the CTAs, which are
+// all within about a round of each other in the list, share the tiles of few heads in L2); inside a group the unit (query
+// tile pair, key tile) with the most work comes first for every head of the group, then the next unit, and so on.
+// BH heads are cut into n_groups groups whose sizes differ by at most one head (the larger groups first).
+struct HeadGroups {
+    int BH, n_groups, units_per_head;
+};
+// item index -> rank of the unit inside its head (0 = first in the list) and head
+__device__ __forceinline__ void locate_item(const HeadGroups& hg, int idx, int& unit_rank, int& bh) {
+    const int base = hg.BH / hg.n_groups, rem = hg.BH - base * hg.n_groups;
+    const int big = (base + 1) * hg.units_per_head, cut = rem * big;
+    int h0, hn, r;
+    if (idx < cut) {
+        const int grp = idx / big;
+        h0 = grp * (base + 1); hn = base + 1; r = idx - grp * big;
+    } else {
+        const int j = idx - cut, small = base * hg.units_per_head, grp = j / small;
+        h0 = rem * (base + 1) + grp * base; hn = base; r = j - grp * small;
+    }
+    unit_rank = r / hn;
+    bh = h0 + (r - unit_rank * hn);
+}
+
 // ---- proxy / tcgen05 fences ---------------------------------------------------
 // Generic-proxy writes to shared memory -> visible to the async proxy (TMA, MMA).
 __device__ __forceinline__ void fence_proxy_async_smem() {
