@@ -346,7 +346,7 @@ def finish(args, cfg, world, n, T, D, K, value, ms_step, fwd_ms_max, bwd_ms_max,
                       unit="TFLOP/s", frac=achieved / pk["bf16_sustained"], of=pk["source"],
                       algorithmic_flops_per_launch=bwd_flops_rank, traffic=TRAFFIC_BYTES_PER_ELEMENT * n * T * D if TRAFFIC_BYTES_PER_ELEMENT else None,
                       traffic_source="ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on c3 "
-                                     "(profiles/attn_bwd_kernel_c3_bf16_T8192_D128.md), scaled by elements per launch"),
+                                     "(profiles/attn_bwd_persist_kernel_c3_bf16_T8192_D128.md), scaled by elements per launch"),
     )
     if world == 1 and not args.no_cpu_baseline:
         try:
@@ -363,11 +363,11 @@ def finish(args, cfg, world, n, T, D, K, value, ms_step, fwd_ms_max, bwd_ms_max,
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of one attn_bwd_kernel launch per element of a [heads, T, D] operand, from the
-# ncu capture summarised in profiles/attn_bwd_kernel_c3_bf16_T8192_D128.md: (404.8 + 225.4) MB over
+# DRAM bytes (read + write) of one attn_bwd_persist_kernel launch per element of a [heads, T, D] operand, from the
+# ncu capture summarised in profiles/attn_bwd_persist_kernel_c3_bf16_T8192_D128.md: (407.2 + 227.3) MB over
 # 32 heads x 8192 x 128 elements.  DRAM traffic of this kernel is proportional to the elements it touches
 # (each operand is read once from DRAM; re-reads by other CTAs of a head hit L2).
-TRAFFIC_BYTES_PER_ELEMENT = (404.804608e6 + 225.368320e6) / (32 * 8192 * 128)
+TRAFFIC_BYTES_PER_ELEMENT = (407.163392e6 + 227.260672e6) / (32 * 8192 * 128)
 
 
 def main():
