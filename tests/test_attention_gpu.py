@@ -176,6 +176,44 @@ def test_config5_shape_replicated_heads(oracle_mod):
     assert_close([np_(o), np_(dq), np_(dk), np_(dv)], refs, TOL["bf16"], oracle_mod, "c5 prototypes")
 
 
+def _torch_fp32_reference(q, k, v, do):
+    """Causal attention and its gradients in plain fp32 torch ops on the GPU (scores materialised)."""
+    q, k, v, do = (t.float() for t in (q, k, v, do))
+    T, D = q.shape[-2], q.shape[-1]
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    s = (q @ k.transpose(-1, -2)) / D ** 0.5
+    s = s.masked_fill(torch.triu(torch.ones(T, T, device=q.device, dtype=torch.bool), 1), float("-inf"))
+    o = torch.softmax(s, -1) @ v
+    o.backward(do)
+    return o.detach(), q.grad, k.grad, v.grad
+
+
+def test_random_shapes_and_item_counts():
+    """bf16 kernels walk a list of work items with one CTA per SM, drawing items from a counter: shapes with fewer items
+    than SMs, one more or one less than a whole round, many light heads, and seeded random (B, H, T, D); every output
+    against fp32 torch ops, and O / dK / dV bitwise equal between two runs (dQ is a floating-point reduction)."""
+    import random
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    rng = random.Random(7)
+    shapes = [(1, 2, 129, 128), (sms, 1, 128, 128), (sms + 1, 1, 128, 64), (sms - 1, 1, 256, 128), (37, 4, 256, 128),
+              (2, 74, 384, 64), (3, 50, 257, 128), (1, 1, 2048, 64)]
+    shapes += [(rng.randint(1, 6), rng.randint(1, 6), rng.randint(2, 1500), rng.choice([64, 128])) for _ in range(24)]
+    g = torch.Generator(device="cuda").manual_seed(11)
+    for (B, H, T, D) in shapes:
+        q, k, v = (torch.randn(B, H, T, D, device="cuda", generator=g).to(torch.bfloat16) for _ in range(3))
+        do = (torch.randn(B, H, T, D, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+        o, lse = A.attention_forward(q, k, v)
+        grads = A.attention_backward(q, k, v, o, do, lse)
+        o2, lse2 = A.attention_forward(q, k, v)
+        grads2 = A.attention_backward(q, k, v, o2, do, lse2)
+        torch.cuda.synchronize()
+        A.check_device_status()
+        assert torch.equal(o, o2) and torch.equal(grads[1], grads2[1]) and torch.equal(grads[2], grads2[2]), (B, H, T, D)
+        for name, x, r in zip(("O", "dQ", "dK", "dV"), (o,) + tuple(grads), _torch_fp32_reference(q, k, v, do)):
+            err = ((x.float() - r).norm() / r.norm()).item()
+            assert err < TOL["bf16"], f"{(B, H, T, D)} {name}: rel err {err:.3e}"
+
+
 def test_backward_is_linear_in_dO():
     q, k, v, do = (torch.from_numpy(a).cuda().to(torch.bfloat16) for a in make_inputs(1, 2, 512, 128, 8, dtype="bf16"))
     o, lse = A.attention_forward(q, k, v)
