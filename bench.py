@@ -36,6 +36,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c5", help="workload from inferno_b200.synth.CONFIGS (bf16 ones)")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-heads-per-chunk", type=int, default=64, help="heads per chunk of the host pipeline")
+    ap.add_argument("--e2e-nbuf", type=int, default=2, help="device staging sets of the host pipeline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -298,8 +300,8 @@ def run_ours(args, cfg):
 
 def measure_e2e(args, torch, dist, A, HostAttention, dev, world, n, T, D, operands, o, barrier, total_flops):
     q, k, v, do = operands
-    hc = max(1, min(n, 64))
-    pipe = HostAttention(hc, T, D, torch.bfloat16, dev)
+    hc = max(1, min(n, args.e2e_heads_per_chunk))
+    pipe = HostAttention(hc, T, D, torch.bfloat16, dev, nbuf=args.e2e_nbuf)
     hin = [torch.empty((n, 1, T, D), dtype=torch.bfloat16).pin_memory() for _ in range(4)]
     hout = [torch.empty((n, 1, T, D), dtype=torch.bfloat16).pin_memory() for _ in range(4)]
     for h_, d_ in zip(hin, (q, k, v, do)):
