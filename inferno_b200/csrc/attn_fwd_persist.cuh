@@ -247,10 +247,12 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 #pragma unroll
                 for (int e = 0; e < 8; ++e) mx8[e] = s[e];
 #pragma unroll
-                for (int e = 8; e < BN; e += 8)
+                for (int u = 0; u < 8; ++u) mx8[u] = fmaxf(mx8[u], s[8 + u]);
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) mx8[u] = fmaxf(mx8[u], s[e + u]);
-                const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+                for (int e = 16; e < BN; e += 16)
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) mx8[u] = fmax3(mx8[u], s[e + u], s[e + 8 + u]);
+                const float mx = fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]));
                 float mx_s = mx * c;
                 if (mx == -INFINITY) mx_s = m_used;                    // fully masked row in this tile
                 if (j == 0) {
