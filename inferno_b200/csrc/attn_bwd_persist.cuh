@@ -2,7 +2,7 @@
 //
 // Same block algorithm, warp roles, shared-memory and TMEM plan as attn_bwd_kernel (attn_bwd.cuh, which names the
 // reference nodes the backward replaces).  One CTA per SM walks a list of work items (one item = one 128-row key / value
-// tile of one head, tiles with the longest walk first), and all mbarrier phases run on from item to item (each role
+// tile of one head), and all mbarrier phases run on from item to item (each role
 // counts the query blocks it has handled), so that
 //   * the TMA warp loads the next item's K and V tiles as soon as the last MMA of the current item has completed, i.e.
 //     under the epilogue that turns dK / dV into bf16 and stores them, and its first Q / dO blocks as soon as the
@@ -11,6 +11,10 @@
 //     an item wait for the epilogue to have read the accumulators out of TMEM;
 //   * a CTA's launch, barrier set-up, TMEM allocation and tear-down are paid once per SM instead of once per item.
 // A non-persistent CTA spends about 11 us outside its steady state (17 % of an average item at T = 4096).
+// Items are drawn, not assigned: a CTA starts on item blockIdx.x and its TMA thread draws every further index from a
+// counter in global memory (ItemRing in sm100_ptx.cuh hands it to the other roles).  The list runs over groups of
+// consecutive heads (locate_item) so that the CTAs share the Q / dO tiles and the fp32 dQ accumulator of few heads in L2 at
+// a time, and inside a group from key tile 0 (the longest walk) to the last.
 #pragma once
 
 #include "attn_bwd.cuh"

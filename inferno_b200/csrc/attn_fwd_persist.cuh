@@ -2,7 +2,7 @@
 //
 // Same tile algorithm, warp roles and TMEM plan as attn_fwd_kernel (attn_fwd.cuh, which names the reference code the
 // forward replaces: InfernoApp/main.cpp:737-754).  The difference is the outer structure: one CTA per SM walks a list of
-// work items (one item = two adjacent 128-row query tiles of one head, heaviest items first), and the roles run ahead of
+// work items (one item = two adjacent 128-row query tiles of one head), and the roles run ahead of
 // each other across item boundaries:
 //   * the TMA warp loads the next item's Q tiles and first K tile as soon as the last S = Q K^T of the current item has
 //     been issued and completed (barrier q_free), i.e. during the current item's last key tile and epilogue;
@@ -12,6 +12,10 @@
 // A non-persistent CTA pays about 7 us per item for launch, the first loads, the pipeline fill and the epilogue, which is
 // 20 % of an average item at T = 4096 and half of one at T = 1024; here most of it runs under another item's work.
 // All mbarrier phases run on from item to item; each role derives them from its own counters.
+// Items are drawn, not assigned: a CTA starts on item blockIdx.x and its TMA thread draws every further index from a
+// counter in global memory (ItemRing in sm100_ptx.cuh hands it to the other roles), so CTAs that drew short walks draw more
+// of them.  The list runs over groups of consecutive heads (locate_item) so that the CTAs share the K / V tiles of few
+// heads in L2 at a time, and inside a group from the longest walk to the shortest.
 #pragma once
 
 #include "attn_fwd.cuh"
