@@ -4,11 +4,12 @@
 // reference nodes the backward replaces).  One CTA per SM walks a list of work items (one item = one 128-row key / value
 // tile of one head), and all mbarrier phases run on from item to item (each role
 // counts the query blocks it has handled), so that
-//   * the TMA warp loads the next item's K and V tiles as soon as the last MMA of the current item has completed, i.e.
-//     under the epilogue that turns dK / dV into bf16 and stores them, and its first Q / dO blocks as soon as the
-//     epilogue's staging (which borrows the Q / dO ring) has been read out;
-//   * the MMA warp starts the next item's S^T / dP^T as soon as those tiles have landed; only the first dK / dV MMAs of
-//     an item wait for the epilogue to have read the accumulators out of TMEM;
+//   * the TMA warp loads the next item's K and V tiles as soon as the last MMA of the current item has completed, and
+//     keeps the Q / dO ring running straight into the next item;
+//   * the four drain warps, not the compute warps, turn dK / dV into bf16 (staged in their own dQ^T staging tile, which
+//     has the size of one bf16 dK / dV tile) and store them, so the compute warps go straight on to the next item's first
+//     blocks and the MMA warp to its S^T / dP^T / dQ^T; only an item's first dK / dV MMAs wait until the drain warps have
+//     read the accumulators out of TMEM;
 //   * a CTA's launch, barrier set-up, TMEM allocation and tear-down are paid once per SM instead of once per item.
 // A non-persistent CTA spends about 11 us outside its steady state (17 % of an average item at T = 4096).
 // Items are drawn, not assigned: a CTA starts on item blockIdx.x and its TMA thread draws every further index from a
@@ -46,9 +47,8 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     uint64_t* dq_full = pds_full + 2;       // [2]   MMA commit: dQ^T in TMEM (and the dS^T smem tile is free)
     uint64_t* dq_empty = dq_full + 2;       // [2]   drain warps: dQ^T copied to registers
     uint64_t* dkv_full = dq_empty + 2;      // [1]   MMA commit: every MMA of the item has completed (dK, dV final; K, V tiles free)
-    uint64_t* dkv_free = dkv_full + 1;      // [1]   compute warps (8): dK, dV read out of TMEM
-    uint64_t* ring_free = dkv_free + 1;     // [1]   the two dK / dV stores have read their staging out of the Q / dO ring
-    uint64_t* item_bars = ring_free + 1;    // [4]   item ring: full[2], empty[2]
+    uint64_t* dkv_free = dkv_full + 1;      // [1]   drain warps (4): dK, dV read out of TMEM
+    uint64_t* item_bars = dkv_free + 1;    // [4]   item ring: full[2], empty[2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(item_bars + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const ItemRing items{item_bars, item_bars + 2, abort_flag + 1};
@@ -81,8 +81,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             mbar_init(&dq_full[b], 1); mbar_init(&dq_empty[b], 4);
         }
         mbar_init(dkv_full, 1);
-        mbar_init(dkv_free, 8);
-        mbar_init(ring_free, 2);
+        mbar_init(dkv_free, 4);
         item_ring_init(items, 13);               // readers: the MMA warp, eight compute warps, four drain warps
         fence_mbar_init();
     }
@@ -120,7 +119,6 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 }
                 idx = static_cast<int>(gridDim.x) + drawn;
                 item_ring_publish(items, ni, idx, ab);
-                if (ni > 0) mbar_wait(ring_free, (ni - 1) & 1, ab, 13);         // the previous epilogue's staging has left the ring
                 for (int it = 0; it < item.nblk; ++it, ++g) {
                     const int s = g % NS;
                     const int m = item.m0 + it;
@@ -171,11 +169,11 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 const uint32_t lQ_mn = lQ0 + s * kStage + kToMN, lDO_mn = lDO0 + s * kStage + kToMN;
                 const uint32_t t_st = tmem + TR::TM_ST + b * 64, t_dp = tmem + TR::TM_DP + b * 64;
                 mbar_wait(&pds_full[b], (gb >> 1) & 1, ab, 22);
-                // the item's first dK / dV MMAs overwrite the accumulators: the previous epilogue must have read them
-                if (it == 0 && ni > 0) mbar_wait(dkv_free, (ni - 1) & 1, ab, 26);
                 tc_fence_after_sync();
                 bwd_issue_dq<TR>(t_dp, lK_mn, lDS, leader);                            // dQ^T over the consumed dP^T buffer
                 if (leader) umma_commit(&dq_full[b]);
+                // the item's first dK / dV MMAs overwrite the accumulators: the previous epilogue must have read them
+                if (it == 0 && ni > 0) { mbar_wait(dkv_free, (ni - 1) & 1, ab, 26); tc_fence_after_sync(); }
                 bwd_issue_acc<TR>(tmem + TR::TM_DK, t_st, 1, lQ_mn, it > 0, leader);   // dK += dS^T Q
                 bwd_issue_acc<TR>(tmem + TR::TM_DV, t_st, 0, lDO_mn, it > 0, leader);  // dV += P^T dO
                 if (leader) umma_commit(&qdo_empty[s]);
@@ -279,58 +277,6 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             }
             g0 += nblk;
 
-            // ---- epilogue of the item: warps 0-3 write dV, warps 4-7 write dK (scaled) ----
-            mbar_wait(dkv_full, ni & 1, ab, 33);
-            tc_fence_after_sync();
-            {
-            const uint32_t t_acc = tmem + (h ? TR::TM_DK : TR::TM_DV) + lane_base;
-            const float mul = h ? prm.scale : 1.f;
-            uint8_t* stage = sQ + h * TR::OUT_TILE;
-#pragma unroll
-            for (int cc = 0; cc < D; cc += 32) {
-                uint32_t rr[32];
-                tmem_ld_x32(t_acc + cc, rr);
-                tmem_wait_ld();
-                if (cc + 32 == D) {
-                    // dK / dV are in registers: the next item's first MMAs may overwrite the accumulators
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(dkv_free);
-                }
-                if constexpr (!TR::SPLIT) {
-                    const int panel = cc / 64, chunk0 = (cc % 64) / 8;
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint4 v;
-                        v.x = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 0]) * mul, __uint_as_float(rr[q4 * 8 + 1]) * mul);
-                        v.y = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 2]) * mul, __uint_as_float(rr[q4 * 8 + 3]) * mul);
-                        v.z = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 4]) * mul, __uint_as_float(rr[q4 * 8 + 5]) * mul);
-                        v.w = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 6]) * mul, __uint_as_float(rr[q4 * 8 + 7]) * mul);
-                        *reinterpret_cast<uint4*>(stage + panel * TR::KV_PANEL + sw128_offset(r, chunk0 + q4)) = v;
-                    }
-                } else {
-                    const int panel = cc / 32;     // 32 fp32 columns = one 128-byte panel row
-#pragma unroll
-                    for (int q4 = 0; q4 < 8; ++q4) {
-                        uint4 v;
-                        v.x = __float_as_uint(__uint_as_float(rr[q4 * 4 + 0]) * mul);
-                        v.y = __float_as_uint(__uint_as_float(rr[q4 * 4 + 1]) * mul);
-                        v.z = __float_as_uint(__uint_as_float(rr[q4 * 4 + 2]) * mul);
-                        v.w = __float_as_uint(__uint_as_float(rr[q4 * 4 + 3]) * mul);
-                        *reinterpret_cast<uint4*>(stage + panel * TR::KV_PANEL + sw128_offset(r, q4)) = v;
-                    }
-                }
-            }
-            fence_proxy_async_smem();
-            asm volatile("bar.sync %0, 128;" ::"r"(1 + h) : "memory");
-            if ((tid & 127) == 0) {
-                for (int p = 0; p < TR::OUT_PANELS; ++p)
-                    tma_store_4d(h ? &tm_dk : &tm_dv, stage + p * TR::KV_PANEL, p * TR::OUT_PANEL_ELEMS, n * BKV, hd, bt);
-                tma_store_commit();
-                tma_store_wait_read_all();
-                mbar_arrive(ring_free);              // the producer may load the next item's Q / dO blocks over the staging
-            }
-            }
         }
     } else if (warp < 12) {
         // ------------------------------ drain dQ^T ------------------------------
@@ -374,6 +320,49 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 }
             }
             g0 += item.nblk;
+
+            // ---- epilogue of the item: dV, then dK (scaled), one key row per thread, staged as bf16 in the dQ^T staging tile
+            // (same size) and stored by TMA.  The compute warps are already on the next item's first blocks.
+            mbar_wait(dkv_full, nd & 1, ab, 41);
+            tc_fence_after_sync();
+            const int r = wq * 32 + lane;
+            uint8_t* stage_b = reinterpret_cast<uint8_t*>(stage);
+#pragma unroll
+            for (int hsel = 0; hsel < 2; ++hsel) {
+                const uint32_t t_acc = tmem + (hsel ? TR::TM_DK : TR::TM_DV) + lane_base;
+                const float mul = hsel ? prm.scale : 1.f;
+                if (issuer) tma_store_wait_read_all();           // the previous reduction / store has read the staging tile
+                asm volatile("bar.sync 3, 128;" ::: "memory");
+#pragma unroll
+                for (int cc = 0; cc < D; cc += 32) {
+                    uint32_t rr[32];
+                    tmem_ld_x32(t_acc + cc, rr);
+                    tmem_wait_ld();
+                    if (hsel == 1 && cc + 32 == D) {
+                        // dK / dV are in registers or staged: the next item's first dK / dV MMAs may overwrite the accumulators
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(dkv_free);
+                    }
+                    const int panel = cc / 64, chunk0 = (cc % 64) / 8;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 v;
+                        v.x = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 0]) * mul, __uint_as_float(rr[q4 * 8 + 1]) * mul);
+                        v.y = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 2]) * mul, __uint_as_float(rr[q4 * 8 + 3]) * mul);
+                        v.z = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 4]) * mul, __uint_as_float(rr[q4 * 8 + 5]) * mul);
+                        v.w = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 6]) * mul, __uint_as_float(rr[q4 * 8 + 7]) * mul);
+                        *reinterpret_cast<uint4*>(stage_b + panel * TR::KV_PANEL + sw128_offset(r, chunk0 + q4)) = v;
+                    }
+                }
+                fence_proxy_async_smem();
+                asm volatile("bar.sync 3, 128;" ::: "memory");
+                if (issuer) {
+                    for (int p = 0; p < TR::OUT_PANELS; ++p)
+                        tma_store_4d(hsel ? &tm_dk : &tm_dv, stage_b + p * TR::KV_PANEL, p * TR::OUT_PANEL_ELEMS, item.n * BKV, item.hd, item.bt);
+                    tma_store_commit();
+                }
+            }
         }
         if (issuer) tma_store_wait_read_all();
     }
