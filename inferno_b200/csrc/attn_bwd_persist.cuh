@@ -30,6 +30,9 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                         const __grid_constant__ CUtensorMap tm_dq, BwdParams prm, int n_items, int n_groups, int* next_item) {
     static_assert(!TR::SPLIT, "bf16 operands only");
     constexpr int D = TR::D, BKV = TR::BKV, BQ = TR::BQ, NS = TR::NS;
+    // groups of four queries (of the eight a compute thread handles per block) whose lse / delta values are fetched early;
+    // measured best: 6 at D = 128, 4 at D = 64 (more costs registers: the D = 64 variant starts to spill)
+    constexpr int kPre = (D == 128) ? 6 : 4;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* sK = smem + TR::OFF_K;
@@ -208,6 +211,14 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 const uint32_t t_st = tmem + TR::TM_ST + b * 64 + h * 32 + lane_base;
                 const uint32_t t_dp = tmem + TR::TM_DP + b * 64 + h * 32 + lane_base;
                 mbar_wait(&qdo_full[s], (gb / NS) & 1, ab, 30);      // lse / delta visible
+                // the first 16 queries' -lse*log2e and -delta now, under the wait for S^T / dP^T: with the MMA operand reads
+                // loading the shared-memory pipe these broadcast loads take a few hundred cycles when issued in the element loop
+                float4 nl_pre[kPre], nd_pre[kPre];
+#pragma unroll
+                for (int e4 = 0; e4 < kPre; ++e4) {
+                    nl_pre[e4] = reinterpret_cast<const float4*>(v_lse)[e4];
+                    nd_pre[e4] = reinterpret_cast<const float4*>(v_del)[e4];
+                }
                 mbar_wait(&sdp_full[b], (gb >> 1) & 1, ab, 31);
                 tc_fence_after_sync();
             uint32_t sr[32], dr[32];
@@ -227,7 +238,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
                 for (int e4 = 0; e4 < 8; ++e4) {
-                    const float4 nl = v_lse4[e4], nd = v_del4[e4];   // broadcast 16-byte loads: 4 query columns each
+                    const float4 nl = e4 < kPre ? nl_pre[e4 < kPre ? e4 : 0] : v_lse4[e4], nd = e4 < kPre ? nd_pre[e4 < kPre ? e4 : 0] : v_del4[e4];   // broadcast 16-byte loads: 4 query columns each
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
                         const int e = e4 * 4 + half * 2;
@@ -262,13 +273,11 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 tmem_st_x16(t_dp + 16, dl);
             }
                 // the single dS^T smem tile is free once dQ^T of the previous block (of this or the previous item) has completed
+                // (a second tile, which would fit exactly, was measured: no gain)
                 if (gb >= 1) mbar_wait(&dq_full[(gb - 1) & 1], ((gb - 1) >> 1) & 1, ab, 32);
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
+            for (int c4 = 0; c4 < 4; ++c4)
                 *reinterpret_cast<uint4*>(sDS + sw128_offset(r, h * 4 + c4)) = make_uint4(dk[4 * c4], dk[4 * c4 + 1], dk[4 * c4 + 2], dk[4 * c4 + 3]);
-                if constexpr (TR::SPLIT)
-                    *reinterpret_cast<uint4*>(sDS + TR::DS_PART + sw128_offset(r, h * 4 + c4)) = make_uint4(dl[4 * c4], dl[4 * c4 + 1], dl[4 * c4 + 2], dl[4 * c4 + 3]);
-            }
                 tmem_wait_st();
                 fence_proxy_async_smem();
                 tc_fence_before_sync();
