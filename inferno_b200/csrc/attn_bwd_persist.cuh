@@ -33,6 +33,9 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     // groups of four queries (of the eight a compute thread handles per block) whose lse / delta values are fetched early;
     // measured best: 6 at D = 128, 4 at D = 64 (more costs registers: the D = 64 variant starts to spill)
     constexpr int kPre = (D == 128) ? 6 : 4;
+    // D = 64: S^T is handed to the compute warps before dP^T has been issued, so that their exponentials run under it (+8 %);
+    // at D = 128, where the MMA side paces the block, the extra commit and wait bought nothing and one hand-off is used
+    constexpr bool kSplitHandoff = (D == 64);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* sK = smem + TR::OFF_K;
@@ -45,13 +48,14 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     uint64_t* kv_full = bars;               // [1]   K, V of an item
     uint64_t* qdo_full = bars + 1;          // [NS]  TMA: Q, dO tiles + staged lse/delta
     uint64_t* qdo_empty = qdo_full + NS;    // [NS]  MMA commit: block consumed
-    uint64_t* sdp_full = qdo_empty + NS;    // [2]   MMA commit: S^T and dP^T of a block are in TMEM
+    uint64_t* sdp_full = qdo_empty + NS;    // [2]   MMA commit: S^T of a block is in TMEM (dP^T follows: dp_full)
     uint64_t* pds_full = sdp_full + 2;      // [2]   compute warps: P^T, dS^T written (TMEM + smem)
     uint64_t* dq_full = pds_full + 2;       // [2]   MMA commit: dQ^T in TMEM (and the dS^T smem tile is free)
     uint64_t* dq_empty = dq_full + 2;       // [2]   drain warps: dQ^T copied to registers
     uint64_t* dkv_full = dq_empty + 2;      // [1]   MMA commit: every MMA of the item has completed (dK, dV final; K, V tiles free)
     uint64_t* dkv_free = dkv_full + 1;      // [1]   drain warps (4): dK, dV read out of TMEM
-    uint64_t* item_bars = dkv_free + 1;    // [4]   item ring: full[2], empty[2]
+    uint64_t* dp_full = dkv_free + 1;       // [2]   MMA commit: dP^T of a block is in TMEM
+    uint64_t* item_bars = dp_full + 2;    // [4]   item ring: full[2], empty[2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(item_bars + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const ItemRing items{item_bars, item_bars + 2, abort_flag + 1};
@@ -80,7 +84,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         mbar_init(kv_full, 1);
         for (int s = 0; s < NS; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(&sdp_full[b], 1); mbar_init(&pds_full[b], 8);
+            mbar_init(&sdp_full[b], 1); mbar_init(&dp_full[b], 1); mbar_init(&pds_full[b], 8);
             mbar_init(&dq_full[b], 1); mbar_init(&dq_empty[b], 4);
         }
         mbar_init(dkv_full, 1);
@@ -153,9 +157,10 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             mbar_wait(&qdo_full[s], (gb / NS) & 1, ab, 21);
             tc_fence_after_sync();
             bwd_issue_kmajor<TR>(tmem + TR::TM_ST + b * 64, lK, lQ0 + s * kStage, leader);
+            if (kSplitHandoff && leader) umma_commit(&sdp_full[b]);    // the compute warps start on the exponentials while dP^T is still to come
             if (gb >= 2) { mbar_wait(&dq_empty[b], ((gb - 2) >> 1) & 1, ab, 24); tc_fence_after_sync(); }
             bwd_issue_kmajor<TR>(tmem + TR::TM_DP + b * 64, lV, lDO0 + s * kStage, leader);
-            if (leader) umma_commit(&sdp_full[b]);
+            if (leader) umma_commit(kSplitHandoff ? &dp_full[b] : &sdp_full[b]);
         };
         uint32_t g0 = 0;                                                            // global index of the item's first block
         int ni = 0;
@@ -223,27 +228,28 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 tc_fence_after_sync();
             uint32_t sr[32], dr[32];
             tmem_ld_x32(t_st, sr);
-            tmem_ld_x32(t_dp, dr);
             tmem_wait_ld();
             const bool diag = prm.causal && (m * BQ < (n + 1) * BKV);
             const int q0 = m * BQ + h * 32;
             const bool masked = diag || tail_tile;             // uniform per block: most blocks take the unmasked path
-            uint32_t pk[16], dk[16], pl[16], dl[16];
+            uint32_t pk[16], dk[16];
             const uint64_t c2 = pack_f32x2(c, c);
             const float4* v_lse4 = reinterpret_cast<const float4*>(v_lse);
             const float4* v_del4 = reinterpret_cast<const float4*>(v_del);
             // The masked and the unmasked block are two copies of the loop: a branch inside the loop body would cut it
             // into one basic block per element pair and expose the full FFMA -> MUFU -> convert latency 16 times.
-            auto body = [&](auto masked_tag) {
+            // Part 1, as soon as S^T is there: P^T = exp2(c S^T - lse) (kept in sr as fp32 bits, and packed).  The masked and the
+            // unmasked block are two copies of the loop: a branch inside the loop body would cut it into one basic block per
+            // element pair and expose the full FFMA -> MUFU -> convert latency 16 times.
+            auto body_p = [&](auto masked_tag) {
                 constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
                 for (int e4 = 0; e4 < 8; ++e4) {
-                    const float4 nl = e4 < kPre ? nl_pre[e4 < kPre ? e4 : 0] : v_lse4[e4], nd = e4 < kPre ? nd_pre[e4 < kPre ? e4 : 0] : v_del4[e4];   // broadcast 16-byte loads: 4 query columns each
+                    const float4 nl = e4 < kPre ? nl_pre[e4 < kPre ? e4 : 0] : v_lse4[e4];   // broadcast 16-byte loads: 4 query columns each
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
                         const int e = e4 * 4 + half * 2;
                         const uint64_t nl2 = half ? pack_f32x2(nl.z, nl.w) : pack_f32x2(nl.x, nl.y);
-                        const uint64_t nd2 = half ? pack_f32x2(nd.z, nd.w) : pack_f32x2(nd.x, nd.y);
                         float x0, x1;
                         unpack_f32x2(ffma2(pack_f32x2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])), c2, nl2), x0, x1);
                         float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
@@ -251,27 +257,35 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                             if (row_dead || (diag && kv_g > q0 + e)) p0 = 0.f;
                             if (row_dead || (diag && kv_g > q0 + e + 1)) p1 = 0.f;
                         }
-                        const uint64_t p2 = pack_f32x2(p0, p1);
-                        float d0, d1;
-                        unpack_f32x2(fmul2(p2, fadd2(pack_f32x2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])), nd2)), d0, d1);
+                        sr[e] = __float_as_uint(p0);
+                        sr[e + 1] = __float_as_uint(p1);
                         pk[e >> 1] = pack_bf16x2(p0, p1);
-                        dk[e >> 1] = pack_bf16x2(d0, d1);
-                        if constexpr (TR::SPLIT) {
-                            pl[e >> 1] = pack_bf16x2(p0 - __uint_as_float(pk[e >> 1] << 16), p1 - __uint_as_float(pk[e >> 1] & 0xffff0000u));
-                            dl[e >> 1] = pack_bf16x2(d0 - __uint_as_float(dk[e >> 1] << 16), d1 - __uint_as_float(dk[e >> 1] & 0xffff0000u));
-                        }
                     }
                 }
             };
-            if (masked) body(MaskedTag<true>{}); else body(MaskedTag<false>{});
+            if (masked) body_p(MaskedTag<true>{}); else body_p(MaskedTag<false>{});
             tmem_st_x16(t_st, pk);
-            if constexpr (!TR::SPLIT) {
-                tmem_st_x16(t_st + 16, dk);
-            } else {
-                tmem_st_x16(t_st + 16, pl);
-                tmem_st_x16(t_dp, dk);
-                tmem_st_x16(t_dp + 16, dl);
+            // Part 2, once dP^T is there: dS^T = P^T o (dP^T - delta)
+            if constexpr (kSplitHandoff) {
+                mbar_wait(&dp_full[b], (gb >> 1) & 1, ab, 34);
+                tc_fence_after_sync();
             }
+            tmem_ld_x32(t_dp, dr);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e4 = 0; e4 < 8; ++e4) {
+                const float4 nd = e4 < kPre ? nd_pre[e4 < kPre ? e4 : 0] : v_del4[e4];
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int e = e4 * 4 + half * 2;
+                    const uint64_t nd2 = half ? pack_f32x2(nd.z, nd.w) : pack_f32x2(nd.x, nd.y);
+                    const uint64_t p2 = pack_f32x2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1]));
+                    float d0, d1;
+                    unpack_f32x2(fmul2(p2, fadd2(pack_f32x2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])), nd2)), d0, d1);
+                    dk[e >> 1] = pack_bf16x2(d0, d1);
+                }
+            }
+            tmem_st_x16(t_st + 16, dk);
                 // the single dS^T smem tile is free once dQ^T of the previous block (of this or the previous item) has completed
                 // (a second tile, which would fit exactly, was measured: no gain)
                 if (gb >= 1) mbar_wait(&dq_full[(gb - 1) & 1], ((gb - 1) >> 1) & 1, ab, 32);
