@@ -366,10 +366,10 @@ def finish(args, cfg, world, n, T, D, K, value, ms_step, fwd_ms_max, bwd_ms_max,
 
 
 # DRAM bytes (read + write) of one attn_bwd_persist_kernel launch per element of a [heads, T, D] operand, from the
-# ncu capture summarised in profiles/attn_bwd_persist_kernel_c3_bf16_T8192_D128.md: (407.7 + 229.9) MB over
+# ncu capture summarised in profiles/attn_bwd_persist_kernel_c3_bf16_T8192_D128.md: (408.2 + 230.3) MB over
 # 32 heads x 8192 x 128 elements.  DRAM traffic of this kernel is proportional to the elements it touches
 # (each operand is read once from DRAM; re-reads by other CTAs of a head hit L2).
-TRAFFIC_BYTES_PER_ELEMENT = (407.723520e6 + 229.861120e6) / (32 * 8192 * 128)
+TRAFFIC_BYTES_PER_ELEMENT = (408.220928e6 + 230.287872e6) / (32 * 8192 * 128)
 
 
 def main():
