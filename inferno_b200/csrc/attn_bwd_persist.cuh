@@ -31,8 +31,11 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     static_assert(!TR::SPLIT, "bf16 operands only");
     constexpr int D = TR::D, BKV = TR::BKV, BQ = TR::BQ, NS = TR::NS;
     // groups of four queries (of the eight a compute thread handles per block) whose lse / delta values are fetched early;
-    // measured best: 6 at D = 128, 4 at D = 64 (more costs registers: the D = 64 variant starts to spill)
-    constexpr int kPre = (D == 128) ? 6 : 4;
+    // measured on one GPU with the builds swapped in place: at D = 128 all 8 (+2 % at T >= 4096 over 6, -2.5 % at T = 1024), at
+    // D = 64 4 (6 and 8 cost 3-12 %: the variant starts to spill)
+    constexpr int kPre = (D == 128) ? 8 : 4;
+    // D = 128: wait for the dS^T tile before phase two instead of just before the stores (+0.5-1 %; -3 % at D = 64)
+    constexpr bool kWaitDsEarly = (D == 128);
     // D = 64: S^T is handed to the compute warps before dP^T has been issued, so that their exponentials run under it (+8 %);
     // at D = 128, where the MMA side paces the block, the extra commit and wait bought nothing and one hand-off is used
     constexpr bool kSplitHandoff = (D == 64);
@@ -266,6 +269,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             if (masked) body_p(MaskedTag<true>{}); else body_p(MaskedTag<false>{});
             tmem_st_x16(t_st, pk);
             // Part 2, once dP^T is there: dS^T = P^T o (dP^T - delta)
+            if (kWaitDsEarly && gb >= 1) mbar_wait(&dq_full[(gb - 1) & 1], ((gb - 1) >> 1) & 1, ab, 32);
             if constexpr (kSplitHandoff) {
                 mbar_wait(&dp_full[b], (gb >> 1) & 1, ab, 34);
                 tc_fence_after_sync();
@@ -288,7 +292,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             tmem_st_x16(t_st + 16, dk);
                 // the single dS^T smem tile is free once dQ^T of the previous block (of this or the previous item) has completed
                 // (a second tile, which would fit exactly, was measured: no gain)
-                if (gb >= 1) mbar_wait(&dq_full[(gb - 1) & 1], ((gb - 1) >> 1) & 1, ab, 32);
+                if (!kWaitDsEarly && gb >= 1) mbar_wait(&dq_full[(gb - 1) & 1], ((gb - 1) >> 1) & 1, ab, 32);
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4)
                 *reinterpret_cast<uint4*>(sDS + sw128_offset(r, h * 4 + c4)) = make_uint4(dk[4 * c4], dk[4 * c4 + 1], dk[4 * c4 + 2], dk[4 * c4 + 3]);
