@@ -168,6 +168,14 @@ int ib200_attn_set_timing_events(ib200_event_t fwd_start, ib200_event_t fwd_stop
 int ib200_cast_f32_to_bf16(const float* src, void* dst, size_t n, ib200_stream_t stream);
 int ib200_cast_bf16_to_f32(const void* src, float* dst, size_t n, ib200_stream_t stream);
 
+/* Diagnostic, host only (no device needed): the work-item list the persistent bf16 kernels walk for a problem on a GPU with
+ * `sm_count` SMs.  Item i of the list is unit `units[i]` (forward: pair of 128-row query tiles, backward: 128-row key tile) of
+ * head `heads[i]` (0 <= head < B*H); units are numbered as the tensor is (unit 0 = first rows).  The list runs over groups of
+ * consecutive heads; `*n_groups` receives their number.  At most `capacity` entries are written; the return value is the
+ * number of items of the list, or a negative IB200_ERR_* value.  The reference has no counterpart (it launches one thread
+ * per score row, src/inferno/cuda/cudasoftmax.cu:52-97). */
+int ib200_attn_item_order(int pass, int B, int H, int T, int D, int sm_count, int* heads, int* units, int capacity, int* n_groups);
+
 /* Human-readable name of a status value; never NULL. */
 const char* ib200_status_string(int status);
 

@@ -20,7 +20,7 @@ PASS_FWD, PASS_BWD = 0, 1
 EXPORTS = (
     "ib200_attn_workspace_bytes", "ib200_attn_fwd", "ib200_attn_bwd", "ib200_attn_check",
     "ib200_status_string", "ib200_last_cuda_error", "ib200_version", "ib200_attn_set_timing_events", "ib200_attn_bwd_static", "ib200_attn_fwd_strided", "ib200_attn_bwd_strided", "ib200_gemm_bf16", "ib200_linear_fwd", "ib200_linear_bwd",
-    "ib200_cast_f32_to_bf16", "ib200_cast_bf16_to_f32",
+    "ib200_cast_f32_to_bf16", "ib200_cast_bf16_to_f32", "ib200_attn_item_order",
 )
 
 
@@ -72,6 +72,9 @@ def lib() -> ctypes.CDLL:
         L.ib200_cast_f32_to_bf16.restype = i
         L.ib200_cast_bf16_to_f32.argtypes = [vp, vp, sz, vp]
         L.ib200_cast_bf16_to_f32.restype = i
+        ip = ctypes.POINTER(ctypes.c_int)
+        L.ib200_attn_item_order.argtypes = [i, i, i, i, i, i, ip, ip, i, ip]
+        L.ib200_attn_item_order.restype = i
         L.ib200_attn_check.argtypes = [vp, vp, ctypes.POINTER(i)]
         L.ib200_attn_check.restype = i
         L.ib200_attn_set_timing_events.argtypes = [vp, vp, vp, vp]

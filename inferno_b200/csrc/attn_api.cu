@@ -517,6 +517,27 @@ extern "C" {
 
 int ib200_version(void) { return 1000; }
 
+int ib200_attn_item_order(int pass, int B, int H, int T, int D, int sm_count, int* heads, int* units, int capacity, int* n_groups) {
+    if (B <= 0 || H <= 0 || T <= 0 || sm_count <= 0 || capacity < 0 || (capacity > 0 && (!heads || !units))) return -IB200_ERR_INVALID_ARGUMENT;
+    if (D != 64 && D != 128) return -IB200_ERR_UNSUPPORTED;
+    if (pass != IB200_PASS_FWD && pass != IB200_PASS_BWD) return -IB200_ERR_INVALID_ARGUMENT;
+    const long BH = static_cast<long>(B) * H;
+    const bool fwd = pass == IB200_PASS_FWD;
+    const int per_head = fwd ? (T + 255) / 256 : (T + 127) / 128;       // query-tile pairs / key tiles
+    const long items = per_head * BH;
+    if (BH > 65535 || items > 0x7fffffffL) return -IB200_ERR_UNSUPPORTED;
+    const int groups = persist_head_groups(sm_count, per_head, BH, static_cast<size_t>(T) * D * (fwd ? 4 : 8));
+    if (n_groups) *n_groups = groups;
+    const HeadGroups hg{static_cast<int>(BH), groups, per_head};
+    for (long i = 0; i < items && i < capacity; ++i) {
+        int rank, bh;
+        locate_item(hg, static_cast<int>(i), rank, bh);
+        heads[i] = bh;
+        units[i] = fwd ? per_head - 1 - rank : rank;                      // the longest walk first: last pair / first key tile
+    }
+    return static_cast<int>(items);
+}
+
 int ib200_last_cuda_error(void) { return g_last_cuda_error; }
 
 int ib200_attn_set_timing_events(ib200_event_t fwd_start, ib200_event_t fwd_stop, ib200_event_t bwd_start, ib200_event_t bwd_stop) {

@@ -141,7 +141,7 @@ struct HeadGroups {
     int BH, n_groups, units_per_head;
 };
 // item index -> rank of the unit inside its head (0 = first in the list) and head
-__device__ __forceinline__ void locate_item(const HeadGroups& hg, int idx, int& unit_rank, int& bh) {
+__host__ __device__ __forceinline__ void locate_item(const HeadGroups& hg, int idx, int& unit_rank, int& bh) {
     const int base = hg.BH / hg.n_groups, rem = hg.BH - base * hg.n_groups;
     const int big = (base + 1) * hg.units_per_head, cut = rem * big;
     int h0, hn, r;

@@ -113,6 +113,38 @@ def test_cast_argument_validation(built_lib):
         assert L.ib200_cast_f32_to_bf16(0x10000, 0x20000, 16, None) == _capi.ERR_NO_DEVICE
 
 
+@pytest.mark.parametrize("case", [
+    (0, 64, 16, 4096, 128, 148), (1, 64, 16, 4096, 128, 148), (1, 2, 16, 8192, 128, 148), (0, 16, 12, 1024, 64, 148),
+    (1, 16, 16, 1024, 128, 148), (0, 1, 1, 1, 64, 148), (1, 3, 5, 777, 64, 132), (0, 37, 3, 300, 128, 7),
+])
+def test_item_order_of_persistent_kernels(built_lib, case):
+    """The list the persistent kernels draw from: every (head, unit) exactly once; heads grouped into consecutive runs whose
+    sizes differ by at most one; inside a group the heaviest unit of every head first; at least two rounds of items per group."""
+    pass_, B, H, T, D, sms = case
+    L = _capi.lib()
+    per_head = (T + 255) // 256 if pass_ == 0 else (T + 127) // 128
+    n = B * H * per_head
+    heads, units, groups = (ctypes.c_int * n)(), (ctypes.c_int * n)(), ctypes.c_int(0)
+    assert L.ib200_attn_item_order(pass_, B, H, T, D, sms, heads, units, n, ctypes.byref(groups)) == n
+    items = list(zip(heads, units))
+    assert sorted(items) == [(h, u) for h in range(B * H) for u in range(per_head)]
+    g = groups.value
+    assert 1 <= g <= B * H and (g == 1 or n // g >= 2 * sms)
+    # walk the list group by group
+    base, rem, pos, first_head = (B * H) // g, (B * H) % g, 0, 0
+    for k in range(g):
+        size = base + (1 if k < rem else 0)
+        chunk = items[pos:pos + size * per_head]
+        assert {h for h, _ in chunk} == set(range(first_head, first_head + size))
+        work = [(u if pass_ == 0 else per_head - 1 - u) for _, u in chunk]          # longer walk = more work
+        assert work == sorted(work, reverse=True)
+        pos += size * per_head
+        first_head += size
+    assert pos == n
+    assert L.ib200_attn_item_order(pass_, B, H, T, 96, sms, heads, units, n, None) == -_capi.ERR_UNSUPPORTED
+    assert L.ib200_attn_item_order(7, B, H, T, D, sms, heads, units, n, None) == -_capi.ERR_INVALID_ARGUMENT
+
+
 def test_no_device_fails_loudly(built_lib):
     """With well-formed arguments and no sm_100 device the call reports it; nothing else runs."""
     import torch
