@@ -43,12 +43,18 @@ typedef enum {
 } ib200_status;
 
 enum { IB200_DTYPE_F32 = 0, IB200_DTYPE_BF16 = 1 };
-enum { IB200_MATH_TF32 = 0, IB200_MATH_3XTF32 = 1 }; /* fp32 I/O only; ignored for bf16 */
+/* Arithmetic of the fp32-I/O path (ignored for bf16 I/O).  One mode exists: every fp32 operand x is carried as the
+ * bf16 pair (hi = bf16(x), lo = bf16(x - hi)) and every product is hi*hi + lo*hi + hi*lo on the bf16 tensor pipe with
+ * fp32 accumulation -- the accuracy class of a 3xTF32 scheme (measured normwise error <= 1e-5 against float64) at the
+ * cost of 1.5 single TF32 passes.  A single-pass TF32 mode is not implemented; values other than
+ * IB200_MATH_SPLIT_BF16 are refused with IB200_ERR_UNSUPPORTED. */
+enum { IB200_MATH_SPLIT_BF16 = 0 };
 enum { IB200_PASS_FWD = 0, IB200_PASS_BWD = 1 };
 
 /* Bytes of device scratch the forward (pass 0) or backward (pass 1) needs for
  * this problem.  The caller owns the allocation; the library never allocates or
- * frees device memory.  The first 256 bytes hold the device status word.
+ * frees device memory.  The first 256 bytes are a header (device status word, work counter); the
+ * workspace need not be initialised.
  * Replaces nothing one-to-one: the reference's launchers cudaMalloc their own
  * scratch per call (e.g. src/inferno/cuda/cudamaskedfill.cu:86-164). */
 int ib200_attn_workspace_bytes(int B, int H, int T, int D, int dtype, int pass, size_t* out_bytes);
@@ -138,19 +144,39 @@ int ib200_linear_bwd(const void* x, const void* w, const void* dy, void* dx, voi
  *     when the next begins; the parts that must start from zero are cleared on `stream` by each
  *     call.  Two calls whose kernels may overlap on the GPU (different streams without an ordering
  *     between them) race on it: serialise them.
- *   - ib200_attn_check cannot be used with this entry point (the buffer is not caller-visible).
+ *   - An expired device-side wait is reported by ib200_attn_check_static (the buffer is not
+ *     caller-visible, so ib200_attn_check cannot read its status word).
  * This entry point has no counterpart in the reference. */
 int ib200_attn_bwd_static(const void* q, const void* k, const void* v, const void* o, const void* dO,
                           const float* lse, void* dq, void* dk, void* dv,
                           int B, int H, int T, int D, float scale, int causal, int dtype, int math_mode,
                           ib200_stream_t stream);
 
-/* Synchronises `stream`, then reads the device status word that the kernels of the
- * last call using `workspace` left behind.  Returns IB200_OK, IB200_ERR_DEVICE_TIMEOUT
- * (*device_code receives the site code of the wait that expired) or IB200_ERR_CUDA.
+/* Synchronises `stream`, then reads the device status word in the header of `workspace`.  The
+ * word is sticky: it keeps the site code of the FIRST bounded wait that expired in any forward
+ * or backward call that used this workspace since the last check, so one check after a
+ * forward + backward pair (or after a whole step) sees a failure of any of them; a failure is
+ * reported once and the word is cleared.  Returns IB200_OK, IB200_ERR_DEVICE_TIMEOUT
+ * (*device_code receives the site code) or IB200_ERR_CUDA.
  * The reference's counterpart is check_cuda() -> log + exit
  * (src/inferno/cuda/cudaops.h:198-210); this library reports instead of exiting. */
 int ib200_attn_check(const void* workspace, ib200_stream_t stream, int* device_code);
+
+/* The same check for the calls that have no caller workspace: ib200_attn_bwd_static and the
+ * projection entry points (ib200_gemm_bf16, ib200_linear_fwd, ib200_linear_bwd) record an expired
+ * wait in the header of the library's built-in buffer on the current device; this reads and clears
+ * it after synchronising `stream`.  Same return values as ib200_attn_check.  Replaces the same
+ * check_cuda() convention (src/inferno/cuda/cudaops.h:198-210). */
+int ib200_attn_check_static(ib200_stream_t stream, int* device_code);
+
+/* Self-test of the bounded-wait machinery, for test suites: launches one small CTA that allocates
+ * tensor memory and waits on a barrier nothing ever signals; after `limit_us` microseconds
+ * (1 .. 100000) the wait gives up, the CTA records site code 190 in the header of `workspace`
+ * (at least 256 bytes), releases its tensor memory and exits normally -- no fault, no trap; the
+ * context stays usable.  ib200_attn_check on the workspace then returns
+ * IB200_ERR_DEVICE_TIMEOUT with *device_code == 190.  The reference has no counterpart (its
+ * kernels never wait on each other). */
+int ib200_selftest_wait_expiry(void* workspace, size_t workspace_bytes, unsigned limit_us, ib200_stream_t stream);
 
 /* Observability hook: CUDA events (cudaEvent_t handles, or NULL) that the following calls on this
  * host thread record on their stream immediately before and after the forward main kernel and the

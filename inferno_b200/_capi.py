@@ -14,13 +14,14 @@ OK = 0
 ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_MISALIGNED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE = range(1, 9)
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 DTYPE_F32, DTYPE_BF16 = 0, 1
-MATH_TF32, MATH_3XTF32 = 0, 1
+MATH_SPLIT_BF16 = 0
 PASS_FWD, PASS_BWD = 0, 1
 
 EXPORTS = (
     "ib200_attn_workspace_bytes", "ib200_attn_fwd", "ib200_attn_bwd", "ib200_attn_check",
     "ib200_status_string", "ib200_last_cuda_error", "ib200_version", "ib200_attn_set_timing_events", "ib200_attn_bwd_static", "ib200_attn_fwd_strided", "ib200_attn_bwd_strided", "ib200_gemm_bf16", "ib200_linear_fwd", "ib200_linear_bwd",
-    "ib200_cast_f32_to_bf16", "ib200_cast_bf16_to_f32", "ib200_attn_item_order",
+    "ib200_cast_f32_to_bf16", "ib200_cast_bf16_to_f32", "ib200_attn_item_order", "ib200_attn_check_static",
+    "ib200_selftest_wait_expiry",
 )
 
 
@@ -43,7 +44,7 @@ class Ib200Error(RuntimeError):
 def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
-        path = _build.LIB_PATH
+        path = os.environ.get("IB200_LIB") or _build.LIB_PATH      # IB200_LIB: another build of the same library (e.g. the bounds-checked one)
         if not os.path.isfile(path):
             raise ImportError(
                 f"{path} is missing: build it with `python -m inferno_b200.build` (there is no fallback path)")
@@ -77,6 +78,10 @@ def lib() -> ctypes.CDLL:
         L.ib200_attn_item_order.restype = i
         L.ib200_attn_check.argtypes = [vp, vp, ctypes.POINTER(i)]
         L.ib200_attn_check.restype = i
+        L.ib200_attn_check_static.argtypes = [vp, ctypes.POINTER(i)]
+        L.ib200_attn_check_static.restype = i
+        L.ib200_selftest_wait_expiry.argtypes = [vp, sz, ctypes.c_uint, vp]
+        L.ib200_selftest_wait_expiry.restype = i
         L.ib200_attn_set_timing_events.argtypes = [vp, vp, vp, vp]
         L.ib200_attn_set_timing_events.restype = i
         L.ib200_status_string.argtypes = [i]

@@ -58,6 +58,21 @@ def _check_inputs(*tensors: torch.Tensor):
     return q.shape
 
 
+def _check_like(t: torch.Tensor, q: torch.Tensor, name: str):
+    """Caller-supplied output tensors: same shape, dtype and device as q (any strides the kernels can address)."""
+    if t.shape != q.shape or t.dtype != q.dtype or t.device != q.device:
+        raise ValueError(f"causal_attention: `{name}` must match q in shape, dtype and device")
+    return t
+
+
+def _check_lse(lse: torch.Tensor, q: torch.Tensor):
+    """The log-sum-exp vector is addressed densely by the kernels: fp32, contiguous [B, H, T], on q's device."""
+    B, H, T, _ = q.shape
+    if lse.dtype != torch.float32 or lse.device != q.device or tuple(lse.shape) != (B, H, T) or not lse.is_contiguous():
+        raise ValueError("causal_attention: `lse` must be a contiguous float32 [B, H, T] tensor on q's device")
+    return lse
+
+
 def _layout(t: torch.Tensor) -> _capi.Layout:
     """Strides of a [B, H, T, D] tensor (any view whose last axis is contiguous) for the strided entry points."""
     if t.stride(3) != 1:
@@ -84,7 +99,7 @@ def _raise(rc: int, where: str):
         raise _capi.Ib200Error(rc, where)
 
 
-def attention_forward(q, k, v, scale: float | None = None, causal: bool = True, math_mode: int = _capi.MATH_TF32,
+def attention_forward(q, k, v, scale: float | None = None, causal: bool = True, math_mode: int = _capi.MATH_SPLIT_BF16,
                       out=None, lse=None):
     """Launch the forward kernel.  Returns (o [B,H,T,D], lse [B,H,T] fp32).  Asynchronous on the current stream.
 
@@ -95,9 +110,8 @@ def attention_forward(q, k, v, scale: float | None = None, causal: bool = True, 
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     dt = _DTYPES[q.dtype]
-    o = torch.empty((B, H, T, D), dtype=q.dtype, device=q.device) if out is None else out
-    if lse is None:
-        lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
+    o = torch.empty((B, H, T, D), dtype=q.dtype, device=q.device) if out is None else _check_like(out, q, "out")
+    lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device) if lse is None else _check_lse(lse, q)
     ws = _workspace.get(_capi.workspace_bytes(B, H, T, D, dt, _capi.PASS_FWD), q.device)
     lq, lk, lv, lo = _layout(q), _layout(k), _layout(v), _layout(o)
     with torch.cuda.device(q.device):
@@ -110,7 +124,7 @@ def attention_forward(q, k, v, scale: float | None = None, causal: bool = True, 
 
 
 def attention_backward(q, k, v, o, dO, lse, scale: float | None = None, causal: bool = True,
-                       math_mode: int = _capi.MATH_TF32, dq=None, dk=None, dv=None):
+                       math_mode: int = _capi.MATH_SPLIT_BF16, dq=None, dk=None, dv=None):
     """Launch the backward kernels.  Returns (dq, dk, dv).  Asynchronous on the current stream.
     Operands and outputs may be strided views as in ``attention_forward``."""
     B, H, T, D = _check_inputs(q, k, v, o, dO)
@@ -118,10 +132,11 @@ def attention_backward(q, k, v, o, dO, lse, scale: float | None = None, causal: 
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     dt = _DTYPES[q.dtype]
+    _check_lse(lse, q)
     mk = lambda: torch.empty((B, H, T, D), dtype=q.dtype, device=q.device)
-    dq = mk() if dq is None else dq
-    dk = mk() if dk is None else dk
-    dv = mk() if dv is None else dv
+    dq = mk() if dq is None else _check_like(dq, q, "dq")
+    dk = mk() if dk is None else _check_like(dk, q, "dk")
+    dv = mk() if dv is None else _check_like(dv, q, "dv")
     ws = _workspace.get(_capi.workspace_bytes(B, H, T, D, dt, _capi.PASS_BWD), q.device)
     lays = [_layout(t) for t in (q, k, v, o, dO, dq, dk, dv)]
     with torch.cuda.device(q.device):
@@ -135,7 +150,8 @@ def attention_backward(q, k, v, o, dO, lse, scale: float | None = None, causal: 
 
 
 def check_device_status(device=None) -> None:
-    """Synchronise the current stream and raise if a kernel reported an expired wait."""
+    """Synchronise the current stream and raise if a kernel reported an expired wait.  The status word is sticky:
+    one check after any number of forward / backward calls on this stream sees the first failure among them."""
     import ctypes
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
@@ -198,7 +214,7 @@ class AttentionBackward(torch.autograd.Function):
 
 
 def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float | None = None,
-                     math_mode: int = _capi.MATH_TF32, bthd_out: bool = False) -> torch.Tensor:
+                     math_mode: int = _capi.MATH_SPLIT_BF16, bthd_out: bool = False) -> torch.Tensor:
     """``softmax(mask(q k^T * scale)) v`` with a causal mask; differentiable.  q, k, v: [B,H,T,D] tensors or views."""
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
@@ -206,7 +222,7 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
 
 
 def causal_attention_packed(qkv: torch.Tensor, num_heads: int, scale: float | None = None,
-                            math_mode: int = _capi.MATH_TF32) -> torch.Tensor:
+                            math_mode: int = _capi.MATH_SPLIT_BF16) -> torch.Tensor:
     """Attention straight on the fused projection output: ``qkv`` is [B, T, 3*C] (= [B,T,3,H,D]); returns [B, T, C].
     Replaces slice / contiguous / reshape / transpose / contiguous before the kernels and transpose / contiguous /
     reshape after them (InfernoApp/main.cpp:716-737, 758-761) with stride arithmetic: no copy kernel runs."""

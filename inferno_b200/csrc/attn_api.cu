@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <math.h>
 
+#include <atomic>
+
 #include "attn_aux.cuh"
 #include "attn_bwd.cuh"
 #include "attn_bwd_persist.cuh"
@@ -17,7 +19,6 @@ namespace {
 
 using namespace ib200;
 
-thread_local int g_last_cuda_error = 0;
 thread_local cudaEvent_t g_ev[4] = {nullptr, nullptr, nullptr, nullptr};   // fwd start/stop, bwd start/stop
 
 // Timing events are an observability aid: a handle that has gone stale (the hook is per host thread and a
@@ -29,12 +30,17 @@ inline void record_timing_event(int which, cudaStream_t stream) {
     }
 }
 
-inline bool cuda_ok(cudaError_t e) {
-    if (e == cudaSuccess) return true;
-    g_last_cuda_error = static_cast<int>(e);
-    (void)cudaGetLastError();
-    return false;
+// Checked build: the extents the device-side range checks compare against, set on `stream` ahead of every main kernel
+// (a debugging aid: launches on different streams share the one constant and must not overlap).
+#ifdef IB200_BOUNDS
+int set_bounds(int d0, int d1, int d2, int d3, int rows3, int relaxed, unsigned tmem_cols, int* status, cudaStream_t stream) {
+    const BoundsInfo b{{d0, d1, d2, d3}, rows3, relaxed, tmem_cols, status};
+    return cuda_ok(cudaMemcpyToSymbolAsync(c_bounds, &b, sizeof(b), 0, cudaMemcpyHostToDevice, stream)) ? IB200_OK : IB200_ERR_CUDA;
 }
+#define IB200_SET_BOUNDS(...) do { if (int rc_ = set_bounds(__VA_ARGS__)) return rc_; } while (0)
+#else
+#define IB200_SET_BOUNDS(...) do {} while (0)
+#endif
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -86,6 +92,21 @@ inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 constexpr size_t kHeaderBytes = 256;
 
+// Workspace header: word 0 = device status (sticky: the first expired wait stays recorded until ib200_attn_check
+// has read it), word 1 = draw counter of the persistent kernels (zero at every launch), word 3 = "status word is
+// valid" mark.  A workspace arrives uninitialised, so the mark decides whether word 0 is a status or garbage.
+constexpr int kHeaderMagic = 0x1b200a77;
+__global__ void prepare_header_kernel(int* hdr) {
+    if (threadIdx.x == 0) {
+        if (hdr[3] != kHeaderMagic) { hdr[0] = 0; hdr[3] = kHeaderMagic; }
+        hdr[1] = 0;
+    }
+}
+int prepare_header(void* ws, cudaStream_t stream) {
+    prepare_header_kernel<<<1, 32, 0, stream>>>(static_cast<int*>(ws));
+    return launch_status();
+}
+
 struct Problem {
     long BH, N;        // heads, elements per tensor
     bool f32;
@@ -95,10 +116,11 @@ int check_common(int B, int H, int T, int D, int dtype, int math_mode, int causa
     if (B <= 0 || H <= 0 || T <= 0 || D <= 0) return IB200_ERR_INVALID_ARGUMENT;
     if (dtype != IB200_DTYPE_F32 && dtype != IB200_DTYPE_BF16) return IB200_ERR_INVALID_ARGUMENT;
     if (causal != 0 && causal != 1) return IB200_ERR_INVALID_ARGUMENT;
-    if (dtype == IB200_DTYPE_F32 && math_mode != IB200_MATH_TF32 && math_mode != IB200_MATH_3XTF32) return IB200_ERR_INVALID_ARGUMENT;
+    if (dtype == IB200_DTYPE_F32 && math_mode != IB200_MATH_SPLIT_BF16) return IB200_ERR_UNSUPPORTED;
     if (dtype == IB200_DTYPE_BF16 && D != 64 && D != 128) return IB200_ERR_UNSUPPORTED;
     if (dtype == IB200_DTYPE_F32 && D != 64) return IB200_ERR_UNSUPPORTED;
-    if (static_cast<long>(B) * H > 65535L * 32768L) return IB200_ERR_UNSUPPORTED;
+    // one head per grid row of the helper kernels and of the one-CTA-per-item main kernels
+    if (static_cast<long>(B) * H > 65535L) return IB200_ERR_UNSUPPORTED;
     return IB200_OK;
 }
 
@@ -143,8 +165,8 @@ int launch_fwd(const void* q, const void* q_lo, const void* k, const void* k_lo,
     prm.causal = causal;
     prm.scale_log2 = scale * 1.4426950408889634f;
     const int pairs = (T + 255) / 256;
-    if (BH > 65535) return IB200_ERR_UNSUPPORTED;
     dim3 grid(pairs, static_cast<unsigned>(BH), 1);
+    IB200_SET_BOUNDS(TR::SPLIT ? 64 : TR::D, T, lq.H, static_cast<int>(BH / lq.H), static_cast<int>(BH), 0, TR::TM_COLS, status, stream);
     record_timing_event(0, stream);
     attn_fwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tql, tk, tkl, tv, tvl, to, prm);
     const bool launched = cuda_ok(cudaGetLastError());
@@ -178,7 +200,6 @@ int launch_fwd_persist(const void* q, const void* k, const void* v, void* o, con
         return IB200_ERR_CUDA;
     if (!cuda_ok(cudaFuncSetAttribute(attn_fwd_persist_kernel<TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::SMEM_BYTES)))
         return IB200_ERR_CUDA;
-    if (BH > 65535) return IB200_ERR_UNSUPPORTED;
     FwdPersistParams pp;
     pp.p.lse = lse;
     pp.p.status = status;
@@ -196,6 +217,7 @@ int launch_fwd_persist(const void* q, const void* k, const void* v, void* o, con
     const int grid = static_cast<int>(items < sms ? items : sms);
     pp.n_groups = persist_head_groups(sms, pp.pairs_per_head, BH, static_cast<size_t>(T) * D * 4 /*K, V*/);
     pp.next_item = status + 1;              // second word of the workspace header, zeroed with it before every launch
+    IB200_SET_BOUNDS(D, T, lq.H, static_cast<int>(BH / lq.H), static_cast<int>(BH), 0, TR::TM_COLS, status, stream);
     record_timing_event(0, stream);
     attn_fwd_persist_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tk, tv, to, pp);
     const bool launched = cuda_ok(cudaGetLastError());
@@ -243,8 +265,8 @@ int launch_bwd(const void* const q[2], const void* const k[2], const void* const
     prm.causal = causal;
     prm.scale = scale;
     prm.scale_log2 = scale * 1.4426950408889634f;
-    if (BH > 65535) return IB200_ERR_UNSUPPORTED;
     dim3 grid((T + TR::BKV - 1) / TR::BKV, static_cast<unsigned>(BH), 1);
+    IB200_SET_BOUNDS(TR::D, T, lq.H, static_cast<int>(BH / lq.H), static_cast<int>(BH), 0, TR::TM_COLS, status, stream);
     record_timing_event(2, stream);
     attn_bwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq[0], tq[1], tk[0], tk[1], tv[0], tv[1], tdo[0], tdo[1], tdk, tdv, tdq, prm);
     const bool launched = cuda_ok(cudaGetLastError());
@@ -276,7 +298,6 @@ int launch_bwd_persist(const void* q, const void* k, const void* v, const void* 
     }
     if (!cuda_ok(cudaFuncSetAttribute(attn_bwd_persist_kernel<TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::SMEM_BYTES)))
         return IB200_ERR_CUDA;
-    if (BH > 65535) return IB200_ERR_UNSUPPORTED;
     BwdParams prm;
     prm.nlse2 = nlse2;
     prm.ndelta = ndelta;
@@ -294,6 +315,7 @@ int launch_bwd_persist(const void* q, const void* k, const void* v, const void* 
     if (cuda_ok(cudaGetDevice(&dev))) (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = static_cast<int>(items < sms ? items : sms);
     const int n_groups = persist_head_groups(sms, (T + TR::BKV - 1) / TR::BKV, BH, static_cast<size_t>(T) * TR::D * 8 /*Q, dO, fp32 dQ*/);
+    IB200_SET_BOUNDS(TR::D, T, lq.H, static_cast<int>(BH / lq.H), static_cast<int>(BH), 0, TR::TM_COLS, status, stream);
     record_timing_event(2, stream);
     attn_bwd_persist_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdk, tdv, tdq, prm, static_cast<int>(items), n_groups,
                                                                                status + 1 /*draw counter: header word zeroed before every launch*/);
@@ -319,8 +341,9 @@ int launch_bwd_all(const void* q, const void* k, const void* v, const void* o, c
     const size_t vec_bytes = round_up(static_cast<size_t>(BH) * T_pad * 4, 256);
     float* ndelta = reinterpret_cast<float*>(after_acc);
     float* nlse2 = reinterpret_cast<float*>(after_acc + vec_bytes);
-    if (!cuda_ok(cudaMemsetAsync(ws, 0, kHeaderBytes + round_up(N * 4, 256), stream))) return IB200_ERR_CUDA;
-    int rc;
+    int rc = prepare_header(ws, stream);
+    if (rc) return rc;
+    if (!cuda_ok(cudaMemsetAsync(dq_acc, 0, round_up(N * 4, 256), stream))) return IB200_ERR_CUDA;
     if (f32) {
         uint8_t* base = after_acc + 2 * vec_bytes;
         const size_t slab = round_up(N * 2, 256);
@@ -371,20 +394,49 @@ int resolve_layout(const ib200_layout* in, int H, int T, int D, bool f32, RowLay
 static __device__ __align__(256) unsigned char g_static_scratch[IB200_STATIC_SCRATCH_BYTES];
 
 constexpr int kMaxDevices = 64;
-void* g_static_scratch_addr[kMaxDevices] = {};
+// Filled on first use per device.  Two host threads that race on the first call both look the address up and both
+// store the same value, so a relaxed atomic is all the cache needs.
+std::atomic<void*> g_static_scratch_addr[kMaxDevices];
 
 // Device address of the static scratch on the current device (set-up on first use per device).
 int static_scratch(void** out) {
     int dev = 0;
     if (!cuda_ok(cudaGetDevice(&dev))) return IB200_ERR_NO_DEVICE;
     if (dev < 0 || dev >= kMaxDevices) return IB200_ERR_UNSUPPORTED;
-    if (!g_static_scratch_addr[dev]) {
-        void* p = nullptr;
+    void* p = g_static_scratch_addr[dev].load(std::memory_order_relaxed);
+    if (!p) {
         if (!cuda_ok(cudaGetSymbolAddress(&p, g_static_scratch)) || !p) return IB200_ERR_CUDA;
-        g_static_scratch_addr[dev] = p;
+        g_static_scratch_addr[dev].store(p, std::memory_order_relaxed);
     }
-    *out = g_static_scratch_addr[dev];
+    *out = p;
     return IB200_OK;
+}
+
+// Self-test of the bounded-wait path, without any fault: one CTA allocates TMEM, warp 1 waits on an mbarrier that
+// nothing ever arrives on and gives up after `limit_ns`, warp 2 waits on the same barrier with the product limit and
+// must come back as soon as warp 1 has raised the CTA's abort flag; the CTA then frees its TMEM and exits normally.
+__global__ void __launch_bounds__(128, 1) wait_expiry_probe_kernel(int* status, unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) { abort_flag = 0; mbar_init(&bar, 1); fence_mbar_init(); }
+    if (warp == 0) { tmem_alloc(&tmem_slot, 32); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    AbortCtx ab{&abort_flag, status};
+    if (warp == 1) mbar_wait_limit(&bar, 0, ab, 90, limit_ns);
+    if (warp == 2) mbar_wait(&bar, 0, ab, 91);
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_slot, 32);
+}
+
+bool header_is_builtin(const void* header) {
+    for (int d = 0; d < kMaxDevices; ++d)
+        if (header && g_static_scratch_addr[d].load(std::memory_order_relaxed) == header) return true;
+    return false;
 }
 
 template <bool A_MN, bool B_MN>
@@ -416,9 +468,12 @@ int launch_gemm(const void* a, const void* b, void* c, const float* bias, int M,
     prm.bias = bias;
     prm.M = M; prm.N = N; prm.K = K;
     prm.splits = splits;
-    prm.status = nullptr;
+    // an expired wait is recorded in the status word of the library's built-in buffer (read by ib200_attn_check_static)
+    void* builtin = nullptr;
+    prm.status = static_scratch(&builtin) == IB200_OK ? static_cast<int*>(builtin) : nullptr;
     const long units = tiles * splits;
     const int grid = static_cast<int>(units < sms ? units : sms);       // persistent: one CTA per SM
+    IB200_SET_BOUNDS(0, 0, 0, 0, 0, 1, TR::TM_COLS, prm.status, stream);
     gemm_bf16_kernel<A_MN, B_MN><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(ta, tb, tc, prm);
     return cuda_ok(cudaGetLastError()) ? IB200_OK : IB200_ERR_CUDA;
 }
@@ -457,7 +512,7 @@ int fwd_core(const void* q, const void* k, const void* v, void* o, float* lse, c
 
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     int* status = reinterpret_cast<int*>(ws);
-    if (!cuda_ok(cudaMemsetAsync(ws, 0, kHeaderBytes, stream))) return IB200_ERR_CUDA;
+    if ((rc = prepare_header(ws, stream))) return rc;
     if (f32) {
         // fp32 operands are carried as dense (hi, lo) bf16 pairs
         const size_t slab = round_up(N * 2, 256);
@@ -515,7 +570,7 @@ int bwd_core(const void* q, const void* k, const void* v, const void* o, const v
 
 extern "C" {
 
-int ib200_version(void) { return 1000; }
+int ib200_version(void) { return 1001; }
 
 int ib200_attn_item_order(int pass, int B, int H, int T, int D, int sm_count, int* heads, int* units, int capacity, int* n_groups) {
     if (B <= 0 || H <= 0 || T <= 0 || sm_count <= 0 || capacity < 0 || (capacity > 0 && (!heads || !units))) return -IB200_ERR_INVALID_ARGUMENT;
@@ -595,7 +650,7 @@ const char* ib200_status_string(int status) {
 int ib200_attn_workspace_bytes(int B, int H, int T, int D, int dtype, int pass, size_t* out_bytes) {
     if (!out_bytes) return IB200_ERR_INVALID_ARGUMENT;
     if (pass != IB200_PASS_FWD && pass != IB200_PASS_BWD) return IB200_ERR_INVALID_ARGUMENT;
-    int rc = check_common(B, H, T, D, dtype, IB200_MATH_TF32, 1);
+    int rc = check_common(B, H, T, D, dtype, IB200_MATH_SPLIT_BF16, 1);
     if (rc != IB200_OK) return rc;
     const long BH = static_cast<long>(B) * H;
     const long N = BH * T * D;
@@ -678,14 +733,41 @@ int ib200_linear_bwd(const void* x, const void* w, const void* dy, void* dx, voi
     return IB200_OK;
 }
 
-int ib200_attn_check(const void* workspace, ib200_stream_t stream_, int* device_code) {
-    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-    if (!workspace) return IB200_ERR_INVALID_ARGUMENT;
-    int code = 0;
-    if (!cuda_ok(cudaMemcpyAsync(&code, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream))) return IB200_ERR_CUDA;
+static int read_and_clear_status(void* header, cudaStream_t stream, int* device_code) {
+    int hdr[4] = {0, 0, 0, 0};
+    if (!cuda_ok(cudaMemcpyAsync(hdr, header, sizeof(hdr), cudaMemcpyDeviceToHost, stream))) return IB200_ERR_CUDA;
     if (!cuda_ok(cudaStreamSynchronize(stream))) return IB200_ERR_CUDA;
+    // a caller workspace that no call has prepared yet holds no status
+    const int code = (hdr[3] == kHeaderMagic || header_is_builtin(header)) ? hdr[0] : 0;
     if (device_code) *device_code = code;
-    return code == 0 ? IB200_OK : IB200_ERR_DEVICE_TIMEOUT;
+    if (code == 0) return IB200_OK;
+    if (!cuda_ok(cudaMemsetAsync(header, 0, sizeof(int), stream))) return IB200_ERR_CUDA;      // reported once
+    return IB200_ERR_DEVICE_TIMEOUT;
+}
+
+int ib200_attn_check(const void* workspace, ib200_stream_t stream, int* device_code) {
+    if (!workspace) return IB200_ERR_INVALID_ARGUMENT;
+    return read_and_clear_status(const_cast<void*>(workspace), reinterpret_cast<cudaStream_t>(stream), device_code);
+}
+
+int ib200_selftest_wait_expiry(void* workspace, size_t workspace_bytes, unsigned limit_us, ib200_stream_t stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (!workspace || !aligned16(workspace) || workspace_bytes < kHeaderBytes) return IB200_ERR_WORKSPACE;
+    if (limit_us == 0 || limit_us > 100000u) return IB200_ERR_INVALID_ARGUMENT;
+    int rc = device_ok();
+    if (rc != IB200_OK) return rc;
+    if ((rc = prepare_header(workspace, stream))) return rc;
+    IB200_SET_BOUNDS(0, 0, 0, 0, 0, 1, 32, static_cast<int*>(workspace), stream);
+    wait_expiry_probe_kernel<<<1, 128, 0, stream>>>(static_cast<int*>(workspace), 1000ull * limit_us);
+    return launch_status();
+}
+
+int ib200_attn_check_static(ib200_stream_t stream, int* device_code) {
+    int rc = device_ok();
+    if (rc != IB200_OK) return rc;
+    void* builtin = nullptr;
+    if ((rc = static_scratch(&builtin)) != IB200_OK) return rc;
+    return read_and_clear_status(builtin, reinterpret_cast<cudaStream_t>(stream), device_code);
 }
 
 }  // extern "C"

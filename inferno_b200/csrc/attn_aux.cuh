@@ -17,6 +17,17 @@
 
 namespace ib200 {
 
+// cudaError_t of the most recent failing CUDA call on this host thread (what ib200_last_cuda_error returns).
+inline thread_local int g_last_cuda_error = 0;
+inline bool cuda_ok(cudaError_t e) {
+    if (e == cudaSuccess) return true;
+    g_last_cuda_error = static_cast<int>(e);
+    (void)cudaGetLastError();
+    return false;
+}
+constexpr int kErrCuda = 5;      // IB200_ERR_CUDA
+inline int launch_status() { return cuda_ok(cudaGetLastError()) ? 0 : kErrCuda; }
+
 // Where the rows of a [B, H, T, D] operand live: element strides of the batch, head and token axes
 // (the D elements of a row are contiguous).  Dense row-major is {H*T*D, T*D, D}; a q/k/v slice of a packed
 // [B, T, 3, H, D] projection is {T*3*H*D, D, 3*H*D}.
@@ -66,7 +77,7 @@ inline int launch_split_bf16(const float* in, void* hi, void* lo, const RowLayou
     if (bx > 64) bx = 64;                                    // grid-stride inside a head beyond that
     dim3 grid(bx, static_cast<unsigned>(heads), 1);
     split_bf16_kernel<<<grid, kAuxThreads, 0, stream>>>(in, reinterpret_cast<uint4*>(hi), reinterpret_cast<uint4*>(lo), lin, T, D);
-    return cudaGetLastError() == cudaSuccess ? 0 : 5;
+    return launch_status();
 }
 
 // Dense casts between fp32 and bf16 (round to nearest even), 8 elements per thread: for callers whose tensors are
@@ -158,7 +169,7 @@ inline int launch_delta(const void* o, const void* dO, const float* lse, float* 
     constexpr int RPB = kAuxThreads / (D / (F32 ? 4 : 8));
     dim3 grid((T_pad + RPB * 4 - 1) / (RPB * 4), static_cast<unsigned>(heads), 1);
     delta_kernel<D, F32><<<grid, kAuxThreads, 0, stream>>>(o, dO, lse, ndelta, nlse2, lo, ldo, T, T_pad);
-    return cudaGetLastError() == cudaSuccess ? 0 : 5;
+    return launch_status();
 }
 
 // out[row, :] = scale * acc[row, :], 8 elements per thread; acc is dense [heads, T, D], out follows `lout`.
@@ -210,7 +221,7 @@ inline int launch_dq_finish(const float* acc, void* out, float scale, const RowL
     const int n8 = T * (D / 8);
     dim3 grid((n8 + kAuxThreads * 4 - 1) / (kAuxThreads * 4), static_cast<unsigned>(heads), 1);
     dq_finish_kernel<D, F32><<<grid, kAuxThreads, 0, stream>>>(reinterpret_cast<const float4*>(acc), out, scale, lout, T);
-    return cudaGetLastError() == cudaSuccess ? 0 : 5;
+    return launch_status();
 }
 
 }  // namespace ib200

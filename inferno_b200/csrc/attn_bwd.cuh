@@ -375,9 +375,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (it >= 1) mbar_wait(&dq_full[(it - 1) & 1], ((it - 1) >> 1) & 1, ab, 32);
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) {
-                *reinterpret_cast<uint4*>(sDS + sw128_offset(r, h * 4 + c4)) = make_uint4(dk[4 * c4], dk[4 * c4 + 1], dk[4 * c4 + 2], dk[4 * c4 + 3]);
+                st_shared_sw128(sDS, r, h * 4 + c4, make_uint4(dk[4 * c4], dk[4 * c4 + 1], dk[4 * c4 + 2], dk[4 * c4 + 3]));
                 if constexpr (TR::SPLIT)
-                    *reinterpret_cast<uint4*>(sDS + TR::DS_PART + sw128_offset(r, h * 4 + c4)) = make_uint4(dl[4 * c4], dl[4 * c4 + 1], dl[4 * c4 + 2], dl[4 * c4 + 3]);
+                    st_shared_sw128(sDS + TR::DS_PART, r, h * 4 + c4, make_uint4(dl[4 * c4], dl[4 * c4 + 1], dl[4 * c4 + 2], dl[4 * c4 + 3]));
             }
             tmem_wait_st();
             fence_proxy_async_smem();
@@ -407,7 +407,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         v.y = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 2]) * mul, __uint_as_float(rr[q4 * 8 + 3]) * mul);
                         v.z = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 4]) * mul, __uint_as_float(rr[q4 * 8 + 5]) * mul);
                         v.w = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 6]) * mul, __uint_as_float(rr[q4 * 8 + 7]) * mul);
-                        *reinterpret_cast<uint4*>(stage + panel * TR::KV_PANEL + sw128_offset(r, chunk0 + q4)) = v;
+                        st_shared_sw128(stage + panel * TR::KV_PANEL, r, chunk0 + q4, v);
                     }
                 } else {
                     const int panel = cc / 32;     // 32 fp32 columns = one 128-byte panel row
@@ -418,7 +418,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         v.y = __float_as_uint(__uint_as_float(rr[q4 * 4 + 1]) * mul);
                         v.z = __float_as_uint(__uint_as_float(rr[q4 * 4 + 2]) * mul);
                         v.w = __float_as_uint(__uint_as_float(rr[q4 * 4 + 3]) * mul);
-                        *reinterpret_cast<uint4*>(stage + panel * TR::KV_PANEL + sw128_offset(r, q4)) = v;
+                        st_shared_sw128(stage + panel * TR::KV_PANEL, r, q4, v);
                     }
                 }
             }

@@ -206,7 +206,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         for (int idx = blockIdx.x; idx < n_items; idx = item_ring_next(items, ni++, ab, lane == 0)) {
             if (*abort_flag != 0) break;
             const Item item = decode(idx);
-            const int n = item.n, m0 = item.m0, nblk = item.nblk, hd = item.hd, bt = item.bt;
+            const int n = item.n, m0 = item.m0, nblk = item.nblk;
             const int kv_g = n * BKV + r;
             const bool row_dead = kv_g >= T;
             const bool tail_tile = (n + 1) * BKV > T;     // this key tile has rows past T
@@ -219,8 +219,9 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 const uint32_t t_st = tmem + TR::TM_ST + b * 64 + h * 32 + lane_base;
                 const uint32_t t_dp = tmem + TR::TM_DP + b * 64 + h * 32 + lane_base;
                 mbar_wait(&qdo_full[s], (gb / NS) & 1, ab, 30);      // lse / delta visible
-                // the first 16 queries' -lse*log2e and -delta now, under the wait for S^T / dP^T: with the MMA operand reads
-                // loading the shared-memory pipe these broadcast loads take a few hundred cycles when issued in the element loop
+                // the block's -lse*log2e and -delta values (kPre groups of four queries) now, under the wait for S^T / dP^T: with
+                // the MMA operand reads loading the shared-memory pipe these broadcast loads take a few hundred cycles when
+                // issued in the element loop
                 float4 nl_pre[kPre], nd_pre[kPre];
 #pragma unroll
                 for (int e4 = 0; e4 < kPre; ++e4) {
@@ -229,73 +230,71 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 }
                 mbar_wait(&sdp_full[b], (gb >> 1) & 1, ab, 31);
                 tc_fence_after_sync();
-            uint32_t sr[32], dr[32];
-            tmem_ld_x32(t_st, sr);
-            tmem_wait_ld();
-            const bool diag = prm.causal && (m * BQ < (n + 1) * BKV);
-            const int q0 = m * BQ + h * 32;
-            const bool masked = diag || tail_tile;             // uniform per block: most blocks take the unmasked path
-            uint32_t pk[16], dk[16];
-            const uint64_t c2 = pack_f32x2(c, c);
-            const float4* v_lse4 = reinterpret_cast<const float4*>(v_lse);
-            const float4* v_del4 = reinterpret_cast<const float4*>(v_del);
-            // The masked and the unmasked block are two copies of the loop: a branch inside the loop body would cut it
-            // into one basic block per element pair and expose the full FFMA -> MUFU -> convert latency 16 times.
-            // Part 1, as soon as S^T is there: P^T = exp2(c S^T - lse) (kept in sr as fp32 bits, and packed).  The masked and the
-            // unmasked block are two copies of the loop: a branch inside the loop body would cut it into one basic block per
-            // element pair and expose the full FFMA -> MUFU -> convert latency 16 times.
-            auto body_p = [&](auto masked_tag) {
-                constexpr bool kMasked = decltype(masked_tag)::value;
+                uint32_t sr[32], dr[32];
+                tmem_ld_x32(t_st, sr);
+                tmem_wait_ld();
+                const bool diag = prm.causal && (m * BQ < (n + 1) * BKV);
+                const int q0 = m * BQ + h * 32;
+                const bool masked = diag || tail_tile;             // uniform per block: most blocks take the unmasked path
+                uint32_t pk[16], dk[16];
+                const uint64_t c2 = pack_f32x2(c, c);
+                const float4* v_lse4 = reinterpret_cast<const float4*>(v_lse);
+                const float4* v_del4 = reinterpret_cast<const float4*>(v_del);
+                // Phase one, as soon as S^T is there: P^T = exp2(c S^T - lse), kept in sr as fp32 bits and packed to bf16.
+                // The masked and the unmasked block are two copies of the loop: a branch inside the loop body would cut it
+                // into one basic block per element pair and expose the full FFMA -> MUFU -> convert latency 16 times.
+                auto body_p = [&](auto masked_tag) {
+                    constexpr bool kMasked = decltype(masked_tag)::value;
+#pragma unroll
+                    for (int e4 = 0; e4 < 8; ++e4) {
+                        const float4 nl = e4 < kPre ? nl_pre[e4 < kPre ? e4 : 0] : v_lse4[e4];   // broadcast 16-byte loads: 4 query columns each
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            const int e = e4 * 4 + half * 2;
+                            const uint64_t nl2 = half ? pack_f32x2(nl.z, nl.w) : pack_f32x2(nl.x, nl.y);
+                            float x0, x1;
+                            unpack_f32x2(ffma2(pack_f32x2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])), c2, nl2), x0, x1);
+                            float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                            if constexpr (kMasked) {
+                                if (row_dead || (diag && kv_g > q0 + e)) p0 = 0.f;
+                                if (row_dead || (diag && kv_g > q0 + e + 1)) p1 = 0.f;
+                            }
+                            sr[e] = __float_as_uint(p0);
+                            sr[e + 1] = __float_as_uint(p1);
+                            pk[e >> 1] = pack_bf16x2(p0, p1);
+                        }
+                    }
+                };
+                if (masked) body_p(MaskedTag<true>{}); else body_p(MaskedTag<false>{});
+                tmem_st_x16(t_st, pk);
+                // Phase two, once dP^T is there: dS^T = P^T o (dP^T - delta).
+                // The single dS^T shared-memory tile is free once dQ^T of the previous block (of this or the previous item) has
+                // completed (a second tile, which would fit exactly, was measured: no gain); at D = 128 that wait comes first.
+                if (kWaitDsEarly && gb >= 1) mbar_wait(&dq_full[(gb - 1) & 1], ((gb - 1) >> 1) & 1, ab, 32);
+                if constexpr (kSplitHandoff) {
+                    mbar_wait(&dp_full[b], (gb >> 1) & 1, ab, 34);
+                    tc_fence_after_sync();
+                }
+                tmem_ld_x32(t_dp, dr);
+                tmem_wait_ld();
 #pragma unroll
                 for (int e4 = 0; e4 < 8; ++e4) {
-                    const float4 nl = e4 < kPre ? nl_pre[e4 < kPre ? e4 : 0] : v_lse4[e4];   // broadcast 16-byte loads: 4 query columns each
+                    const float4 nd = e4 < kPre ? nd_pre[e4 < kPre ? e4 : 0] : v_del4[e4];
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
                         const int e = e4 * 4 + half * 2;
-                        const uint64_t nl2 = half ? pack_f32x2(nl.z, nl.w) : pack_f32x2(nl.x, nl.y);
-                        float x0, x1;
-                        unpack_f32x2(ffma2(pack_f32x2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])), c2, nl2), x0, x1);
-                        float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-                        if constexpr (kMasked) {
-                            if (row_dead || (diag && kv_g > q0 + e)) p0 = 0.f;
-                            if (row_dead || (diag && kv_g > q0 + e + 1)) p1 = 0.f;
-                        }
-                        sr[e] = __float_as_uint(p0);
-                        sr[e + 1] = __float_as_uint(p1);
-                        pk[e >> 1] = pack_bf16x2(p0, p1);
+                        const uint64_t nd2 = half ? pack_f32x2(nd.z, nd.w) : pack_f32x2(nd.x, nd.y);
+                        const uint64_t p2 = pack_f32x2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1]));
+                        float d0, d1;
+                        unpack_f32x2(fmul2(p2, fadd2(pack_f32x2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])), nd2)), d0, d1);
+                        dk[e >> 1] = pack_bf16x2(d0, d1);
                     }
                 }
-            };
-            if (masked) body_p(MaskedTag<true>{}); else body_p(MaskedTag<false>{});
-            tmem_st_x16(t_st, pk);
-            // Part 2, once dP^T is there: dS^T = P^T o (dP^T - delta)
-            if (kWaitDsEarly && gb >= 1) mbar_wait(&dq_full[(gb - 1) & 1], ((gb - 1) >> 1) & 1, ab, 32);
-            if constexpr (kSplitHandoff) {
-                mbar_wait(&dp_full[b], (gb >> 1) & 1, ab, 34);
-                tc_fence_after_sync();
-            }
-            tmem_ld_x32(t_dp, dr);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e4 = 0; e4 < 8; ++e4) {
-                const float4 nd = e4 < kPre ? nd_pre[e4 < kPre ? e4 : 0] : v_del4[e4];
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const int e = e4 * 4 + half * 2;
-                    const uint64_t nd2 = half ? pack_f32x2(nd.z, nd.w) : pack_f32x2(nd.x, nd.y);
-                    const uint64_t p2 = pack_f32x2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1]));
-                    float d0, d1;
-                    unpack_f32x2(fmul2(p2, fadd2(pack_f32x2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])), nd2)), d0, d1);
-                    dk[e >> 1] = pack_bf16x2(d0, d1);
-                }
-            }
-            tmem_st_x16(t_st + 16, dk);
-                // the single dS^T smem tile is free once dQ^T of the previous block (of this or the previous item) has completed
-                // (a second tile, which would fit exactly, was measured: no gain)
+                tmem_st_x16(t_st + 16, dk);
                 if (!kWaitDsEarly && gb >= 1) mbar_wait(&dq_full[(gb - 1) & 1], ((gb - 1) >> 1) & 1, ab, 32);
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4)
-                *reinterpret_cast<uint4*>(sDS + sw128_offset(r, h * 4 + c4)) = make_uint4(dk[4 * c4], dk[4 * c4 + 1], dk[4 * c4 + 2], dk[4 * c4 + 3]);
+                for (int c4 = 0; c4 < 4; ++c4)
+                    st_shared_sw128(sDS, r, h * 4 + c4, make_uint4(dk[4 * c4], dk[4 * c4 + 1], dk[4 * c4 + 2], dk[4 * c4 + 3]));
                 tmem_wait_st();
                 fence_proxy_async_smem();
                 tc_fence_before_sync();
@@ -303,7 +302,6 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 if (lane == 0) mbar_arrive(&pds_full[b]);
             }
             g0 += nblk;
-
         }
     } else if (warp < 12) {
         // ------------------------------ drain dQ^T ------------------------------
@@ -379,7 +377,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                         v.y = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 2]) * mul, __uint_as_float(rr[q4 * 8 + 3]) * mul);
                         v.z = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 4]) * mul, __uint_as_float(rr[q4 * 8 + 5]) * mul);
                         v.w = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 6]) * mul, __uint_as_float(rr[q4 * 8 + 7]) * mul);
-                        *reinterpret_cast<uint4*>(stage_b + panel * TR::KV_PANEL + sw128_offset(r, chunk0 + q4)) = v;
+                        st_shared_sw128(stage_b + panel * TR::KV_PANEL, r, chunk0 + q4, v);
                     }
                 }
                 fence_proxy_async_smem();

@@ -384,7 +384,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         v.y = pack_bf16x2(__uint_as_float(r[q4 * 8 + 2]) * inv_l, __uint_as_float(r[q4 * 8 + 3]) * inv_l);
                         v.z = pack_bf16x2(__uint_as_float(r[q4 * 8 + 4]) * inv_l, __uint_as_float(r[q4 * 8 + 5]) * inv_l);
                         v.w = pack_bf16x2(__uint_as_float(r[q4 * 8 + 6]) * inv_l, __uint_as_float(r[q4 * 8 + 7]) * inv_l);
-                        *reinterpret_cast<uint4*>(stage + panel * TR::PANEL_BYTES + sw128_offset(t, chunk0 + q4)) = v;
+                        st_shared_sw128(stage + panel * TR::PANEL_BYTES, t, chunk0 + q4, v);
                     }
                 } else {
                     // 32 fp32 columns = one 128-byte panel row = 8 chunks of 16 B
@@ -396,7 +396,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         v.y = __float_as_uint(__uint_as_float(r[q4 * 4 + 1]) * inv_l);
                         v.z = __float_as_uint(__uint_as_float(r[q4 * 4 + 2]) * inv_l);
                         v.w = __float_as_uint(__uint_as_float(r[q4 * 4 + 3]) * inv_l);
-                        *reinterpret_cast<uint4*>(stage + panel * TR::PANEL_BYTES + sw128_offset(t, q4)) = v;
+                        st_shared_sw128(stage + panel * TR::PANEL_BYTES, t, q4, v);
                     }
                 }
             }

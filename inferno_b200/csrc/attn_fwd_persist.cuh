@@ -341,7 +341,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                         v.y = pack_bf16x2(__uint_as_float(r[q4 * 8 + 2]) * inv_l, __uint_as_float(r[q4 * 8 + 3]) * inv_l);
                         v.z = pack_bf16x2(__uint_as_float(r[q4 * 8 + 4]) * inv_l, __uint_as_float(r[q4 * 8 + 5]) * inv_l);
                         v.w = pack_bf16x2(__uint_as_float(r[q4 * 8 + 6]) * inv_l, __uint_as_float(r[q4 * 8 + 7]) * inv_l);
-                        *reinterpret_cast<uint4*>(sO + panel * TR::PANEL_BYTES + sw128_offset(t, chunk0 + q4)) = v;
+                        st_shared_sw128(sO + panel * TR::PANEL_BYTES, t, chunk0 + q4, v);
                     }
                 }
                 if (row_g < T) prm.lse[static_cast<size_t>(it.bh) * T + row_g] = (m_used + log2f(l)) * 0.6931471805599453f;

@@ -185,7 +185,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         o.y = pack_bf16x2(__uint_as_float(v[q4 * 8 + 2]) + bs[q4 * 8 + 2], __uint_as_float(v[q4 * 8 + 3]) + bs[q4 * 8 + 3]);
                         o.z = pack_bf16x2(__uint_as_float(v[q4 * 8 + 4]) + bs[q4 * 8 + 4], __uint_as_float(v[q4 * 8 + 5]) + bs[q4 * 8 + 5]);
                         o.w = pack_bf16x2(__uint_as_float(v[q4 * 8 + 6]) + bs[q4 * 8 + 6], __uint_as_float(v[q4 * 8 + 7]) + bs[q4 * 8 + 7]);
-                        *reinterpret_cast<uint4*>(stage + sw128_offset(r, half * 4 + q4)) = o;
+                        st_shared_sw128(stage, r, half * 4 + q4, o);
                     }
                 }
                 if (ch == BN / TR::OUT_CHUNK_COLS - 1) {

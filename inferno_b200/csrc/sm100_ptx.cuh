@@ -20,7 +20,11 @@ namespace ib200 {
 // normal tear-down (TMEM freed) and the host reports an error.
 // ----------------------------------------------------------------------------
 constexpr uint32_t kSpinLimit = 1u << 24;
+#ifdef IB200_BOUNDS
+constexpr unsigned long long kWaitLimitNs = 50000000ull;        // checked build: a skipped copy leaves its barrier waiting; give up after 50 ms
+#else
 constexpr unsigned long long kWaitLimitNs = 4000000000ull;      // 4 s: three orders of magnitude above the longest kernel
+#endif
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
@@ -28,19 +32,61 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
 enum : int {
     kDevOk = 0,
     kDevTimeoutBase = 100,   // 100 + site id of the wait that gave up
+    kDevBoundsBase = 200,    // 200 + kind of access that failed its range check (checked build only)
 };
+
+// ----------------------------------------------------------------------------
+// Checked build (-DIB200_BOUNDS): every TMA copy, tensor-memory access and swizzled shared-memory
+// store below first checks its coordinates / addresses against the extents the host put into
+// c_bounds before the launch.  A violation records kDevBoundsBase + kind in the status word and
+// the access is SKIPPED -- nothing traps or asserts; a skipped load leaves its barrier waiting,
+// the bounded wait gives up, and the kernel runs to its normal tear-down.  The regular build
+// compiles none of this.
+// ----------------------------------------------------------------------------
+#ifdef IB200_BOUNDS
+struct BoundsInfo {
+    int dim[4];            // extents of the operand tensors: {D, T, H, B} (attention) -- unused when relaxed
+    int rows3;             // extent of the last axis of the 3-D dQ accumulator map (B*H)
+    int relaxed;           // 1: only signs and alignment are checked (GEMM: every operand has its own extents)
+    unsigned tmem_cols;    // columns this CTA allocated
+    int* status;
+};
+__constant__ BoundsInfo c_bounds;
+enum : int { kBndTmaLoad = 1, kBndTmaStore = 2, kBndTmaReduce = 3, kBndBulkLoad = 4, kBndTmemLd = 5, kBndTmemSt = 6, kBndMmaDesc = 7, kBndSwizzle = 8 };
+__device__ __forceinline__ bool bounds_ok(bool cond, int kind) {
+    if (cond) return true;
+    if (c_bounds.status) atomicCAS(c_bounds.status, 0, kDevBoundsBase + kind);
+    return false;
+}
+__device__ __forceinline__ bool smem_addr_ok(uint32_t saddr, uint32_t align) {
+    uint32_t total;
+    asm volatile("mov.u32 %0, %%total_smem_size;" : "=r"(total));
+    return saddr < total && (saddr & (align - 1)) == 0;
+}
+__device__ __forceinline__ bool coords4_ok(int c0, int c1, int c2, int c3) {
+    if (c0 < 0 || c1 < 0 || c2 < 0 || c3 < 0 || (c0 & 7)) return false;
+    return c_bounds.relaxed || (c0 < c_bounds.dim[0] && c1 < c_bounds.dim[1] && c2 < c_bounds.dim[2] && c3 < c_bounds.dim[3]);
+}
+__device__ __forceinline__ bool tmem_addr_ok(uint32_t taddr, uint32_t ncols) {
+    return (taddr & 0xffffu) + ncols <= c_bounds.tmem_cols && (taddr >> 16) < 128u;
+}
+#define IB200_CHECKED(cond, kind) if (!bounds_ok((cond), (kind))) return
+#else
+#define IB200_CHECKED(cond, kind)
+#endif
 
 struct AbortCtx {
     volatile int* cta_flag;   // shared memory, one per CTA
     int* status;              // global memory, one per launch (may be null)
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
 
 // ---- mbarrier ---------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -83,7 +129,9 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // Returns false if the wait was abandoned (abort already raised, or limit hit).
 // The CTA abort flag lives in shared memory; it is polled only every 64th failed try so that
 // spinning warps do not load the shared-memory pipe the MMAs and compute warps depend on.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ab, int site) {
+// `limit_ns` is a compile-time constant at every call site of the product kernels (mbar_wait below);
+// only the wait-expiry self-test kernel passes a run-time value.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, const AbortCtx& ab, int site, unsigned long long limit_ns) {
     if (mbar_test_wait(bar, parity)) return true;
     uint32_t spins = 0;
     unsigned long long t_start = 0;
@@ -93,13 +141,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
             if (*ab.cta_flag != 0) return false;
             const unsigned long long now = global_timer_ns();
             if (t_start == 0) t_start = now;
-            if (spins > kSpinLimit || now - t_start > kWaitLimitNs) {
+            if (spins > kSpinLimit || now - t_start > limit_ns) {
                 *ab.cta_flag = 1;
                 if (ab.status) atomicCAS(ab.status, 0, kDevTimeoutBase + site);
                 return false;
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ab, int site) {
+    return mbar_wait_limit(bar, parity, ab, site, kWaitLimitNs);
 }
 
 // ---- work items of a persistent CTA ---------------------------------------------
@@ -175,6 +226,7 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
 // 3-D tile load global -> shared, completion on an mbarrier (transaction bytes).
 // c0 is the innermost coordinate: c0 * elem_size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2) {
+    IB200_CHECKED(coords4_ok(c0, c1, c2, 0) && smem_addr_ok(smem_u32(smem_dst), 1024), kBndTmaLoad);
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
@@ -183,6 +235,7 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
 // Untiled bulk copy global -> shared with mbarrier completion; both addresses 16-byte aligned,
 // size a multiple of 16 bytes.
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+    IB200_CHECKED(smem_addr_ok(smem_u32(smem_dst), 16) && (reinterpret_cast<uint64_t>(gmem_src) & 15u) == 0 && (bytes & 15u) == 0 && bytes > 0, kBndBulkLoad);
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
@@ -192,12 +245,14 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_sr
 // strides are free, which is how operands that live inside a packed [B, T, 3, H, D] projection buffer
 // (or any other layout with contiguous head-dim rows) are read and written in place.
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2, int c3) {
+    IB200_CHECKED(coords4_ok(c0, c1, c2, c3) && smem_addr_ok(smem_u32(smem_dst), 1024), kBndTmaLoad);
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2, int c3) {
+    IB200_CHECKED(coords4_ok(c0, c1, c2, c3) && smem_addr_ok(smem_u32(smem_src), 1024), kBndTmaStore);
     asm volatile(
         "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
         ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
@@ -205,6 +260,7 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* s
 }
 // 3-D tile store shared -> global (rows outside the tensor are clipped).
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2) {
+    IB200_CHECKED(coords4_ok(c0, c1, c2, 0) && smem_addr_ok(smem_u32(smem_src), 1024), kBndTmaStore);
     asm volatile(
         "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
         ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
@@ -212,6 +268,8 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* s
 }
 // 3-D tile reduction shared -> global: global[tile] += shared[tile], element type from the tensor map.
 __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2) {
+    IB200_CHECKED(c0 == 0 && c1 >= 0 && c2 >= 0 && (c_bounds.relaxed || (c1 < c_bounds.dim[1] && c2 < c_bounds.rows3)) &&
+                  smem_addr_ok(smem_u32(smem_src), 128), kBndTmaReduce);
     asm volatile(
         "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
         ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
@@ -236,6 +294,9 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 // ---- MMA issue -----------------------------------------------------------------
 // D[tmem] (+)= A[smem desc] * B[smem desc]; one thread issues for the CTA.
 __device__ __forceinline__ void umma_ss_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    // operand start addresses (descriptor bits 0-13 hold address >> 4) inside the CTA's shared memory; N accumulator columns inside the allocation
+    IB200_CHECKED(smem_addr_ok(static_cast<uint32_t>(adesc & 0x3fffu) << 4, 16) && smem_addr_ok(static_cast<uint32_t>(bdesc & 0x3fffu) << 4, 16) &&
+                  tmem_addr_ok(d_tmem, ((idesc >> 17) & 0x3fu) << 3), kBndMmaDesc);
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
@@ -244,23 +305,11 @@ __device__ __forceinline__ void umma_ss_f16(uint32_t d_tmem, uint64_t adesc, uin
 }
 // D[tmem] (+)= A[tmem] * B[smem desc].
 __device__ __forceinline__ void umma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    IB200_CHECKED(smem_addr_ok(static_cast<uint32_t>(bdesc & 0x3fffu) << 4, 16) && tmem_addr_ok(d_tmem, ((idesc >> 17) & 0x3fu) << 3) &&
+                  tmem_addr_ok(a_tmem, 8), kBndMmaDesc);
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_ss_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_ts_tf32(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
@@ -281,9 +330,9 @@ __device__ __forceinline__ bool elect_one_lane() {
 
 // ---- descriptors ---------------------------------------------------------------
 constexpr uint32_t kMajorK = 0, kMajorMN = 1;
-constexpr uint32_t kFmtBF16 = 1, kFmtTF32 = 2;
+constexpr uint32_t kFmtBF16 = 1;
 
-// Instruction descriptor for kind::f16 / kind::tf32 with fp32 accumulation.
+// Instruction descriptor for kind::f16 with fp32 accumulation.
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t M, uint32_t N, uint32_t a_major, uint32_t b_major) {
     return (1u << 4)                 // accumulator format: f32
            | (fmt << 7)              // A format
@@ -299,17 +348,7 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t M, uint
 //   MN-major (rows = K index, 128 contiguous bytes of M or N per row):
 //       lbo = byte distance between 128-byte column panels along M/N,
 //       sbo = byte distance between 8-row groups along K.
-__device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
-    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
-    d |= static_cast<uint64_t>(1) << 46;   // descriptor version for sm_100
-    d |= static_cast<uint64_t>(2) << 61;   // SWIZZLE_128B
-    return d;
-}
-
-// The same descriptor split into words, so that an MMA issue loop pays one 32-bit add per operand:
+// The descriptor is built from two words, so that an MMA issue loop pays one 32-bit add per operand:
 // the high word is a constant for every 128B-swizzled operand with 1024-byte 8-row groups, and the
 // low word is (address >> 4) | (lbo >> 4) << 16, to which a byte offset adds as (offset >> 4).
 constexpr uint32_t kSdescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
@@ -328,10 +367,23 @@ __host__ __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t
     return row * 128u + ((chunk16 ^ (row & 7u)) << 4);
 }
 
+// 16-byte store into a 128B-swizzled panel ([rows x 128 bytes], 1024-byte aligned).
+__device__ __forceinline__ void st_shared_sw128(uint8_t* panel, uint32_t row, uint32_t chunk16, uint4 v) {
+    IB200_CHECKED(row < 256u && chunk16 < 8u && smem_addr_ok(smem_u32(panel), 1024), kBndSwizzle);
+    *reinterpret_cast<uint4*>(panel + sw128_offset(row, chunk16)) = v;
+}
+
 // ---- TMEM <-> registers --------------------------------------------------------
 // 32x32b shape: the warp reads 32 lanes (its quarter: lanes 32*(warp%4)..+31),
 // thread i gets lane i, N consecutive 32-bit columns.
 __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
+#ifdef IB200_BOUNDS
+    if (!bounds_ok(tmem_addr_ok(taddr, 32), kBndTmemLd)) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) r[e] = 0u;
+        return;
+    }
+#endif
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -343,16 +395,8 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
-__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
 __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    IB200_CHECKED(tmem_addr_ok(taddr, 32), kBndTmemSt);
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -365,6 +409,7 @@ __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[
         : "memory");
 }
 __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    IB200_CHECKED(tmem_addr_ok(taddr, 16), kBndTmemSt);
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
@@ -417,18 +462,4 @@ __device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
-// Adds a byte offset to the start-address field of a shared-memory descriptor (the field holds
-// address >> 4 in its low 14 bits; offsets used here never carry out of it).
-__device__ __forceinline__ uint64_t sdesc_advance(uint64_t desc, uint32_t byte_offset) {
-    return desc + static_cast<uint64_t>(byte_offset >> 4);
-}
-
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(pred));
-    return pred != 0;
-}
-
 }  // namespace ib200

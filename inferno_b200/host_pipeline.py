@@ -28,42 +28,72 @@ class HostAttention:
         self.s_in = torch.cuda.Stream(self.device)
         self.s_run = torch.cuda.Stream(self.device)
         self.s_out = torch.cuda.Stream(self.device)
+        # one event per staging set and pipeline stage, created once: a run records and waits, it creates nothing
+        self.ev_in = [torch.cuda.Event() for _ in range(nbuf)]
+        self.ev_run = [torch.cuda.Event() for _ in range(nbuf)]
+        self.ev_out = [torch.cuda.Event() for _ in range(nbuf)]
+        self.ev_done = torch.cuda.Event()
 
-    def run(self, q, k, v, do, o, dq, dk, dv) -> None:
-        """All arguments: pinned host tensors [heads, 1, T, D] (or any shape with that many elements per
-        head).  Returns after every output has landed in host memory."""
+    def run(self, q, k, v, do, o, dq, dk, dv, wait: bool = True) -> None:
+        """All arguments: pinned host tensors [heads, 1, T, D] (or any shape with that many elements per head).
+        With ``wait`` (the default) the call returns after every output has landed in host memory; with
+        ``wait=False`` the results are only ordered on the caller's current stream, and the host must synchronise
+        that stream (or call ``wait_done``) before it reads the output tensors."""
         heads = q.shape[0]
         main = torch.cuda.current_stream(self.device)
         for s in (self.s_in, self.s_run, self.s_out):
             s.wait_stream(main)
-        in_free = [None] * self.nbuf      # kernels of the chunk that last used this set have read its inputs
-        out_free = [None] * self.nbuf     # results of that chunk have been copied out of this set
+        used = [False] * self.nbuf
+        for ci, h0 in enumerate(range(0, heads, self.hc)):
+            n = min(self.hc, heads - h0)
+            j = ci % self.nbuf
+            b = self.bufs[j]
+            with torch.cuda.stream(self.s_in):
+                if used[j]:
+                    self.s_in.wait_event(self.ev_run[j])       # the kernels of the chunk that last used this set have read its inputs
+                for name, src in (("q", q), ("k", k), ("v", v), ("do", do)):
+                    b[name][:n].copy_(src[h0:h0 + n], non_blocking=True)
+                self.ev_in[j].record(self.s_in)
+            with torch.cuda.stream(self.s_run):
+                self.s_run.wait_event(self.ev_in[j])
+                if used[j]:
+                    self.s_run.wait_event(self.ev_out[j])      # the results of that chunk have been copied out of this set
+                A.attention_forward(b["q"][:n], b["k"][:n], b["v"][:n], out=b["o"][:n], lse=b["lse"][:n])
+                A.attention_backward(b["q"][:n], b["k"][:n], b["v"][:n], b["o"][:n], b["do"][:n], b["lse"][:n],
+                                     dq=b["dq"][:n], dk=b["dk"][:n], dv=b["dv"][:n])
+                self.ev_run[j].record(self.s_run)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.ev_run[j])
+                for name, dst in (("o", o), ("dq", dq), ("dk", dk), ("dv", dv)):
+                    dst[h0:h0 + n].copy_(b[name][:n], non_blocking=True)
+                self.ev_out[j].record(self.s_out)
+            used[j] = True
+        for s in (self.s_in, self.s_run, self.s_out):
+            main.wait_stream(s)
+        self.ev_done.record(main)
+        if wait:
+            self.ev_done.synchronize()
+
+    def wait_done(self) -> None:
+        """Block the host until the last ``run`` has delivered its outputs."""
+        self.ev_done.synchronize()
+
+    def copy_only(self, q, k, v, do, o, dq, dk, dv) -> None:
+        """The copies of ``run`` without its kernels: the same chunks over the same pinned buffers, host-to-device
+        and device-to-host concurrently on the two copy streams.  What this takes is the floor ``run`` is measured
+        against (asynchronous; synchronise the current stream afterwards)."""
+        heads = q.shape[0]
+        main = torch.cuda.current_stream(self.device)
+        for s in (self.s_in, self.s_out):
+            s.wait_stream(main)
         for ci, h0 in enumerate(range(0, heads, self.hc)):
             n = min(self.hc, heads - h0)
             b = self.bufs[ci % self.nbuf]
             with torch.cuda.stream(self.s_in):
-                if in_free[ci % self.nbuf] is not None:
-                    self.s_in.wait_event(in_free[ci % self.nbuf])
                 for name, src in (("q", q), ("k", k), ("v", v), ("do", do)):
                     b[name][:n].copy_(src[h0:h0 + n], non_blocking=True)
-                ev_in = torch.cuda.Event()
-                ev_in.record(self.s_in)
-            with torch.cuda.stream(self.s_run):
-                self.s_run.wait_event(ev_in)
-                if out_free[ci % self.nbuf] is not None:
-                    self.s_run.wait_event(out_free[ci % self.nbuf])
-                A.attention_forward(b["q"][:n], b["k"][:n], b["v"][:n], out=b["o"][:n], lse=b["lse"][:n])
-                A.attention_backward(b["q"][:n], b["k"][:n], b["v"][:n], b["o"][:n], b["do"][:n], b["lse"][:n],
-                                     dq=b["dq"][:n], dk=b["dk"][:n], dv=b["dv"][:n])
-                ev_run = torch.cuda.Event()
-                ev_run.record(self.s_run)
-                in_free[ci % self.nbuf] = ev_run
             with torch.cuda.stream(self.s_out):
-                self.s_out.wait_event(ev_run)
                 for name, dst in (("o", o), ("dq", dq), ("dk", dk), ("dv", dv)):
                     dst[h0:h0 + n].copy_(b[name][:n], non_blocking=True)
-                ev_out = torch.cuda.Event()
-                ev_out.record(self.s_out)
-                out_free[ci % self.nbuf] = ev_out
-        for s in (self.s_in, self.s_run, self.s_out):
+        for s in (self.s_in, self.s_out):
             main.wait_stream(s)

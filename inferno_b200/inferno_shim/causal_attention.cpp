@@ -80,7 +80,7 @@ Tensor causal_attention(const Tensor& q_in, const Tensor& k_in, const Tensor& v_
     Tensor ws = make_workspace(ws_bytes, q.device());
     // the reference launches everything on the legacy default stream
     check(ib200_attn_fwd(dev_ptr(sq), dev_ptr(sk), dev_ptr(sv), dev_ptr(sout), dev_ptr(lse), B, H, T, D, scale, /*causal=*/1,
-                         dtype, IB200_MATH_TF32, dev_ptr(ws), ws_bytes, nullptr),
+                         dtype, IB200_MATH_SPLIT_BF16, dev_ptr(ws), ws_bytes, nullptr),
           "forward");
     if (bf16) check(ib200_cast_bf16_to_f32(dev_ptr(sout), dev_ptr(out), n, nullptr), "widen y");
     int code = 0;
@@ -123,7 +123,7 @@ void AttentionBackward::backward() {
     check(ib200_attn_workspace_bytes(B, H, T, D, dtype, IB200_PASS_BWD, &ws_bytes), "workspace query");
     Tensor ws = make_workspace(ws_bytes, dev);
     check(ib200_attn_bwd(dev_ptr(sq), dev_ptr(sk), dev_ptr(sv), dev_ptr(m_sout), dev_ptr(sdo), dev_ptr(m_lse), dev_ptr(sdq), dev_ptr(sdk),
-                         dev_ptr(sdv), B, H, T, D, m_scale, 1, dtype, IB200_MATH_TF32, dev_ptr(ws), ws_bytes, nullptr),
+                         dev_ptr(sdv), B, H, T, D, m_scale, 1, dtype, IB200_MATH_SPLIT_BF16, dev_ptr(ws), ws_bytes, nullptr),
           "backward");
     if (bf16) {
         check(ib200_cast_bf16_to_f32(dev_ptr(sdq), dev_ptr(dq), n, nullptr), "widen dq");

@@ -65,6 +65,9 @@ def test_workspace_query(built_lib):
     assert L.ib200_attn_workspace_bytes(1, 1, 16, 64, 7, 0, ctypes.byref(out)) == _capi.ERR_INVALID_ARGUMENT
     assert L.ib200_attn_workspace_bytes(1, 1, 16, 64, _capi.DTYPE_BF16, 2, ctypes.byref(out)) == _capi.ERR_INVALID_ARGUMENT
     assert L.ib200_attn_workspace_bytes(1, 1, 16, 64, _capi.DTYPE_BF16, 0, None) == _capi.ERR_INVALID_ARGUMENT
+    # one head per grid row of the helper kernels: more than 65535 heads are refused here, before anything is launched
+    assert L.ib200_attn_workspace_bytes(4096, 16, 16, 64, _capi.DTYPE_BF16, 1, ctypes.byref(out)) == _capi.ERR_UNSUPPORTED
+    assert L.ib200_attn_workspace_bytes(4095, 16, 16, 64, _capi.DTYPE_BF16, 1, ctypes.byref(out)) == _capi.OK
 
 
 def _fwd(L, ptrs, B=1, H=1, T=16, D=64, scale=0.125, causal=1, dtype=_capi.DTYPE_BF16, ws=0x1000, ws_bytes=1 << 20):
@@ -85,6 +88,30 @@ def test_forward_argument_validation(built_lib):
     assert _fwd(L, (0x10004,) + good[1:]) == _capi.ERR_MISALIGNED
     assert _fwd(L, good, ws=None) == _capi.ERR_WORKSPACE
     assert _fwd(L, good, ws_bytes=16) == _capi.ERR_WORKSPACE
+    # fp32 I/O has one arithmetic mode (split bf16); any other value is refused, not silently mapped onto it
+    q, k, v, o, lse = good
+    assert L.ib200_attn_fwd(q, k, v, o, lse, 1, 1, 16, 64, 0.125, 1, _capi.DTYPE_F32, 1, 0x1000, 1 << 20, None) == _capi.ERR_UNSUPPORTED
+
+
+def test_selftest_and_static_check_argument_validation(built_lib):
+    L = _capi.lib()
+    assert L.ib200_selftest_wait_expiry(None, 256, 100, None) == _capi.ERR_WORKSPACE
+    assert L.ib200_selftest_wait_expiry(0x1000, 64, 100, None) == _capi.ERR_WORKSPACE
+    assert L.ib200_selftest_wait_expiry(0x1000, 256, 0, None) == _capi.ERR_INVALID_ARGUMENT
+    assert L.ib200_selftest_wait_expiry(0x1000, 256, 10 ** 6, None) == _capi.ERR_INVALID_ARGUMENT
+    assert L.ib200_attn_check(None, None, None) == _capi.ERR_INVALID_ARGUMENT
+    import torch
+    if not torch.cuda.is_available():
+        assert L.ib200_attn_check_static(None, None) == _capi.ERR_NO_DEVICE
+        assert L.ib200_selftest_wait_expiry(0x1000, 256, 100, None) == _capi.ERR_NO_DEVICE
+
+
+def test_bounds_checked_build_has_the_same_abi(built_lib):
+    """The range-checked build of the library exports exactly the same entry points."""
+    from inferno_b200 import build
+    lib = ctypes.CDLL(build.build(bounds=True))
+    for name in declared_symbols():
+        assert hasattr(lib, name)
 
 
 def test_backward_argument_validation(built_lib):

@@ -80,6 +80,11 @@ def test_static_scratch_backward_matches_regular_entry_point_twice():
         want = _backward_regular(L, q, k, v, o, do, lse, B, H, T, D, code)
         _check(_backward_static(L, q, k, v, o, do, lse, B, H, T, D, code), want)
         _check(_backward_static(L, q, k, v, o, do, lse, B, H, T, D, code), want)   # same problem again, stale scratch
+    # no bounded wait expired in any of those calls: the built-in buffer's status word, which only this reader can see
+    import ctypes
+    dev_code = ctypes.c_int(-1)
+    assert L.ib200_attn_check_static(torch.cuda.current_stream().cuda_stream, ctypes.byref(dev_code)) == _capi.OK
+    assert dev_code.value == 0
 
 
 def test_static_scratch_rejects_problems_beyond_its_capacity():
