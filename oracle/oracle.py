@@ -29,13 +29,26 @@ REF_BIN = os.path.join(_HERE, "_ref", "ref_attention")
 ORACLE_SO = os.path.join(_HERE, "_build", "libattn_oracle.so")
 
 
+def reference_root() -> str | None:
+    """Where the reference's sources lie: the environment variable INFERNO_REF, else the Makefile's default REF."""
+    root = os.environ.get("INFERNO_REF")
+    if not root:
+        with open(os.path.join(_HERE, "Makefile")) as f:
+            for line in f:
+                if line.startswith("REF") and "?=" in line:
+                    root = line.split("?=", 1)[1].strip()
+                    break
+    return root if root and os.path.isdir(os.path.join(root, "src", "inferno")) else None
+
+
 def build(ref: bool | None = None) -> None:
     """Compile the C restatement, and the reference harness when its sources are present."""
     subprocess.run(["make", "-s", "-C", _HERE, "oracle"], check=True)
+    root = reference_root()
     if ref is None:
-        ref = os.path.isdir("/root/reference/src/inferno")
+        ref = root is not None
     if ref:
-        subprocess.run(["make", "-s", "-j8", "-C", _HERE, "ref"], check=True)
+        subprocess.run(["make", "-s", "-j8", "-C", _HERE, "ref", f"REF={root}"], check=True)
 
 
 def have_ref() -> bool:
@@ -51,11 +64,12 @@ def rel_err(x: np.ndarray, ref: np.ndarray) -> float:
     return float(num / den) if den > 0 else float(num)
 
 
-def ref_attention(q, k, v, dO=None, device: str = "cpu", single_pass: bool = False):
+def ref_attention(q, k, v, dO=None, device: str = "cpu", single_pass: bool = False, reps: int = 1):
     """Run the compiled reference.  Returns (o, dq, dk, dv, timings); grads are None if dO is None.
 
     ``single_pass`` runs the backward as one engine pass through the autograd additions of
-    inferno_b200/inferno_shim/autograd_patches.h instead of the two-stage workaround."""
+    inferno_b200/inferno_shim/autograd_patches.h instead of the two-stage workaround.  ``reps`` > 1 repeats the
+    whole pass in the one process and reports the timings of the last (warm) repetition."""
     if not have_ref():
         raise RuntimeError("oracle/_ref/ref_attention is not built (run `make -C oracle ref` where the reference is present)")
     B, H, T, D = q.shape
@@ -67,7 +81,7 @@ def ref_attention(q, k, v, dO=None, device: str = "cpu", single_pass: bool = Fal
                 np.ascontiguousarray(arr, dtype=np.float32).tofile(paths[name])
         prefix = os.path.join(td, "out")
         cmd = [REF_BIN, device, str(B), str(H), str(T), str(D), paths["q"], paths["k"], paths["v"], paths["do"], prefix,
-               ("2" if single_pass else "0") if dO is not None else "1"]
+               ("2" if single_pass else "0") if dO is not None else "1", str(int(reps))]
         res = subprocess.run(cmd, check=True, capture_output=True, text=True, cwd=td)
         timings = json.loads(res.stdout.strip().splitlines()[-1])
         rd = lambda s: np.fromfile(prefix + "." + s + ".bin", dtype=np.float32).reshape(B, H, T, D)

@@ -24,6 +24,7 @@
 // Usage: ref_attention <cpu|cuda> B H T D q.bin k.bin v.bin do.bin out_prefix [mode: 0 fwd+bwd, 1 fwd only, 2 single-pass bwd]
 // Files are raw little-endian fp32, dense row-major [B,H,T,D].
 // Writes <out_prefix>.{o,dq,dk,dv}.bin and prints one JSON line with timings.
+#include <algorithm>
 #include <chrono>
 #include <cmath>
 #include <cstdio>
@@ -67,7 +68,7 @@ static double now_ms() {
 
 int main(int argc, char** argv) {
     if (argc < 11) {
-        std::fprintf(stderr, "usage: %s <cpu|cuda> B H T D q k v do out_prefix [fwd_only]\n", argv[0]);
+        std::fprintf(stderr, "usage: %s <cpu|cuda> B H T D q k v do out_prefix [mode] [reps]\n", argv[0]);
         return 2;
     }
     const bool on_cuda = std::strcmp(argv[1], "cuda") == 0;
@@ -77,11 +78,16 @@ int main(int argc, char** argv) {
     const std::string prefix = argv[10];
     const int mode = argc > 11 ? std::atoi(argv[11]) : 0;
     const bool fwd_only = mode == 1, single_pass = mode == 2;
+    // reps > 1 runs the whole pass that many times in this process and reports the last one: the first pays for the
+    // CUDA context, the cuBLAS handle and the first launch of every kernel (what a timing wants to leave out)
+    const int reps = argc > 12 ? std::max(1, std::atoi(argv[12])) : 1;
     Inferno::Device dev = on_cuda ? Inferno::Device::cuda(0) : Inferno::Device::cpu();
 
     std::vector<float> hq = read_bin(argv[6], n), hk = read_bin(argv[7], n), hv = read_bin(argv[8], n);
     std::vector<float> hdo = fwd_only ? std::vector<float>(n, 0.f) : read_bin(argv[9], n);
 
+    for (int rep = 0; rep < reps; ++rep) {
+    const bool last = rep + 1 == reps;
     Tensor q(Inferno::DType::Float32, hq, {B, H, T, D}, "q", dev, true);
     Tensor k(Inferno::DType::Float32, hk, {B, H, T, D}, "k", dev, true);
     Tensor v(Inferno::DType::Float32, hv, {B, H, T, D}, "v", dev, true);
@@ -103,7 +109,7 @@ int main(int argc, char** argv) {
     Tensor y = Inferno::matmul(p, v, "attn@V");
     if (on_cuda) { (void)y.to(Inferno::Device::cpu()); }  // device->host read = completion point
     double t1 = now_ms();
-    write_tensor(prefix + ".o.bin", y, n);
+    if (last) write_tensor(prefix + ".o.bin", y, n);
 
     double t2 = t1, t3 = t1;
     if (!fwd_only) {
@@ -115,6 +121,7 @@ int main(int argc, char** argv) {
             write_tensor(prefix + ".dk.bin", k.Getgrad().contiguous(), n);
             write_tensor(prefix + ".dv.bin", v.Getgrad().contiguous(), n);
             t3 = now_ms();
+            if (!last) continue;
             std::printf("{\"device\": \"%s\", \"B\": %zu, \"H\": %zu, \"T\": %zu, \"D\": %zu, \"fwd_ms\": %.3f, \"bwd_ms\": %.3f, \"single_pass\": true}\n",
                         argv[1], B, H, T, D, t1 - t0, t3 - t2);
             return 0;
@@ -132,11 +139,16 @@ int main(int argc, char** argv) {
         Tensor dv = v.Getgrad().contiguous();
         if (on_cuda) { (void)dq.to(Inferno::Device::cpu()); (void)dk.to(Inferno::Device::cpu()); (void)dv.to(Inferno::Device::cpu()); }
         t3 = now_ms();
-        write_tensor(prefix + ".dq.bin", dq, n);
-        write_tensor(prefix + ".dk.bin", dk, n);
-        write_tensor(prefix + ".dv.bin", dv, n);
+        if (last) {
+            write_tensor(prefix + ".dq.bin", dq, n);
+            write_tensor(prefix + ".dk.bin", dk, n);
+            write_tensor(prefix + ".dv.bin", dv, n);
+        }
     }
+    if (!last) continue;
     std::printf("{\"device\": \"%s\", \"B\": %zu, \"H\": %zu, \"T\": %zu, \"D\": %zu, \"fwd_ms\": %.3f, \"bwd_ms\": %.3f}\n",
                 argv[1], B, H, T, D, t1 - t0, t3 - t2);
+    return 0;
+    }
     return 0;
 }

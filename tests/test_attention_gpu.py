@@ -5,7 +5,6 @@ Tolerances (normwise relative error ||x - ref||_F / ||ref||_F on O, dQ, dK, dV):
 The reference path itself has no bf16; for bf16 cases the checkers consume the bf16-rounded
 inputs upcast to fp32.
 """
-import json
 import os
 
 import numpy as np
@@ -20,9 +19,7 @@ pytestmark = pytest.mark.gpu
 
 TOL = {"f32": 1e-3, "bf16": 2e-2}
 TDT = {"f32": torch.float32, "bf16": torch.bfloat16}
-GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-with open(os.path.join(GOLDEN, "manifest.json")) as f:
-    MANIFEST = json.load(f)
+from golden_cases import MANIFEST, load_case
 
 
 def run_gpu(q, k, v, do, dt, causal=True):
@@ -44,9 +41,7 @@ def assert_close(outs, refs, tol, orc, what=""):
 @pytest.mark.parametrize("name", [n for n in sorted(MANIFEST) if MANIFEST[n]["D"] in (64, 128)])
 def test_golden_vectors(oracle_mod, name):
     """Outputs of the reference's own code, stored under tests/golden/."""
-    c = MANIFEST[name]
-    q, k, v, do = make_inputs(c["B"], c["H"], c["T"], c["D"], c["seed"], c["qkv_std"], c["do_std"], c["dtype"])
-    gold = np.load(os.path.join(GOLDEN, name + ".npz"))
+    c, (q, k, v, do), gold = load_case(name)
     outs, _ = run_gpu(q, k, v, do, c["dtype"])
     if c["T"] == 1:
         # dQ = dK = 0 exactly in the reference; a relative error is undefined, so compare absolutely

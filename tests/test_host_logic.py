@@ -106,3 +106,45 @@ def test_two_rank_sharding_reproduces_single_process(oracle_mod):
     ret = mgr.dict()
     mp.spawn(_gloo_worker, args=(2, port, ret), nprocs=2, join=True)
     assert ret.get("equal") is True
+
+
+def _bench_validation(rank, world, port, ret):
+    """bench.py's own validation code on CPU tensors: per-head operand streams, float64 spot check, checksum gather."""
+    sys.path.insert(0, ROOT)
+    import bench
+    from inferno_b200.synth import AttnConfig
+    from oracle import oracle as orc
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = AttnConfig("tiny", 2, 3, 40, 16, "bf16", 7, 1.0, 0.5)
+    heads = shard_range(cfg.B * cfg.H, rank, world)
+    host_in = bench.generate_shard(cfg, heads, torch, threads=2)
+    q, k, v, do = (h.float().numpy() for h in host_in)
+    outs = tuple(torch.from_numpy(a).to(torch.bfloat16) for a in orc.oracle_f32(q, k, v, do, scale=cfg.scale, threads=1))
+    val = bench.validate(cfg, torch, dist, world, heads, host_in, outs, 2e-2)
+    if rank == 0:
+        ret[world] = (val["checksum"], val["ok"], val["checksum_heads"], val["heads_checked"])
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def test_bench_validation_digest_does_not_depend_on_the_rank_count(oracle_mod):
+    """The digest the bench prints covers every head's outputs in head order, so a 2-rank run must print the 1-rank value;
+    operands of a head depend on (seed, head) only."""
+    import torch.multiprocessing as mp
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    _bench_validation(0, 1, 0, ret)
+    mp.spawn(_bench_validation, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert ret[1][0] == ret[2][0] and ret[1][1] and ret[2][1]
+    assert ret[1][2] == ret[2][2] == 6 and ret[2][3] == 4
+    from inferno_b200.synth import AttnConfig, make_head_inputs
+    cfg = AttnConfig("tiny", 2, 3, 40, 16, "bf16", 7, 1.0, 0.5)
+    a, b = make_head_inputs(cfg, 4), make_head_inputs(cfg, 4)
+    assert all(np.array_equal(x, y) for x, y in zip(a, b))
+    assert not np.array_equal(make_head_inputs(cfg, 3)[0], a[0])

@@ -1,22 +1,11 @@
 """The CPU checkers against the reference's own outputs (golden vectors) and against each other."""
-import json
 import os
 
 import numpy as np
 import pytest
 
 from inferno_b200.synth import make_inputs
-
-GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-with open(os.path.join(GOLDEN, "manifest.json")) as f:
-    MANIFEST = json.load(f)
-
-
-def load_case(name):
-    c = MANIFEST[name]
-    inputs = make_inputs(c["B"], c["H"], c["T"], c["D"], c["seed"], c["qkv_std"], c["do_std"], c["dtype"])
-    gold = np.load(os.path.join(GOLDEN, name + ".npz"))
-    return c, inputs, gold
+from golden_cases import MANIFEST, load_case
 
 
 @pytest.mark.parametrize("name", sorted(MANIFEST))

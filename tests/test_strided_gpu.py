@@ -71,3 +71,27 @@ def test_misaligned_strides_are_rejected_or_copied():
                                             ctypes.byref(lay), None, None, None, B, H, T, D, 0.125, 1, _capi.DTYPE_BF16, 0,
                                             ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
     assert rc == _capi.ERR_MISALIGNED
+
+
+@pytest.mark.parametrize("B,H,T,D", [(2, 3, 200, 64), (1, 4, 320, 128)])
+def test_packed_autograd_path_against_the_oracle(oracle_mod, B, H, T, D):
+    """`causal_attention_packed` on a [B, T, 3*H*D] projection output, checked directly against the float64 evaluation:
+    the output [B, T, C] and the gradient with respect to the packed buffer."""
+    import numpy as np
+    from inferno_b200.synth import bf16_round
+    rng = np.random.default_rng(77 + T)
+    qkv_np = bf16_round(rng.standard_normal((B, T, 3, H, D), dtype=np.float32))
+    dy_np = bf16_round(0.5 * rng.standard_normal((B, T, H, D), dtype=np.float32))
+    qkv = torch.from_numpy(qkv_np.reshape(B, T, 3 * H * D)).cuda().to(torch.bfloat16).requires_grad_(True)
+    y = A.causal_attention_packed(qkv, H)
+    y.backward(torch.from_numpy(dy_np.reshape(B, T, H * D)).cuda().to(torch.bfloat16))
+    torch.cuda.synchronize()
+    A.check_device_status()
+    q, k, v = (np.ascontiguousarray(qkv_np[:, :, i].transpose(0, 2, 1, 3)) for i in range(3))      # [B,H,T,D]
+    do = np.ascontiguousarray(dy_np.transpose(0, 2, 1, 3))
+    o, dq, dk, dv = oracle_mod.attn_fp64(q, k, v, do)
+    got_y = y.detach().float().cpu().numpy().reshape(B, T, H, D).transpose(0, 2, 1, 3)
+    got_g = qkv.grad.float().cpu().numpy().reshape(B, T, 3, H, D)
+    assert oracle_mod.rel_err(got_y, o) < 2e-2
+    for i, ref in enumerate((dq, dk, dv)):
+        assert oracle_mod.rel_err(got_g[:, :, i].transpose(0, 2, 1, 3), ref) < 2e-2
