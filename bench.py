@@ -552,9 +552,9 @@ def finish(args, cfg, world, n, T, D, K, W, preload_steps, value, ms_step, fwd_m
         clocks=clocks,
         validation=validation,
         e2e=e2e,
-        gpu_launches=(6 if bf16 else 13) * K,
-        kernels_per_step=["prepare_header_kernel (x2)", "attn_fwd_persist_kernel", "delta_kernel", "attn_bwd_persist_kernel", "dq_finish_kernel"] if bf16 else
-                         ["prepare_header_kernel (x2)", "split_bf16_kernel (x2)", "attn_fwd_persist_kernel", "delta_kernel", "attn_bwd_persist_kernel", "dq_finish_kernel"],
+        gpu_launches=5 * K,
+        kernels_per_step=["prepare_header_kernel" if bf16 else "split_bf16_kernel", "attn_fwd_persist_kernel", "bwd_prepass_kernel",
+                          "attn_bwd_persist_kernel", "dq_finish_kernel"],
         roofline=dict(bound="tensor", kernel=bwd_kernel, achieved=achieved, peak=peak,
                       unit="TFLOP/s", frac=achieved / peak, of=pk["source"] + ("" if bf16 else " sustained bf16 / 3: the split schedule issues three bf16 MMAs per product"),
                       algorithmic_flops_per_launch=bwd_flops_rank,

@@ -95,12 +95,8 @@ constexpr size_t kHeaderBytes = 256;
 // Workspace header: word 0 = device status (sticky: the first expired wait stays recorded until ib200_attn_check
 // has read it), word 1 = draw counter of the persistent kernels (zero at every launch), word 3 = "status word is
 // valid" mark.  A workspace arrives uninitialised, so the mark decides whether word 0 is a status or garbage.
-constexpr int kHeaderMagic = 0x1b200a77;
 __global__ void prepare_header_kernel(int* hdr) {
-    if (threadIdx.x == 0) {
-        if (hdr[3] != kHeaderMagic) { hdr[0] = 0; hdr[3] = kHeaderMagic; }
-        hdr[1] = 0;
-    }
+    if (threadIdx.x == 0) prepare_header(hdr);
 }
 int prepare_header(void* ws, cudaStream_t stream) {
     prepare_header_kernel<<<1, 32, 0, stream>>>(static_cast<int*>(ws));
@@ -139,41 +135,6 @@ int device_ok() {
     return major == 10 ? IB200_OK : IB200_ERR_NO_DEVICE;
 }
 
-template <class TR>
-int launch_fwd(const void* q, const void* q_lo, const void* k, const void* k_lo, const void* v, const void* v_lo, void* o,
-               const RowLayout& lq, const RowLayout& lk, const RowLayout& lv, const RowLayout& lo,
-               float* lse, int* status, long BH, int T, float scale, int causal, cudaStream_t stream) {
-    CUtensorMap tq, tql, tk, tkl, tv, tvl, to;
-    if (!make_tmap(&tq, q, false, TR::D, T, lq, BH, 128) || !make_tmap(&tk, k, false, TR::D, T, lk, BH, 128) ||
-        !make_tmap(&tv, v, false, TR::D, T, lv, BH, 128) || !make_tmap(&to, o, TR::SPLIT, TR::D, T, lo, BH, 128))
-        return IB200_ERR_CUDA;
-    if (TR::SPLIT) {
-        if (!make_tmap(&tql, q_lo, false, TR::D, T, lq, BH, 128) || !make_tmap(&tkl, k_lo, false, TR::D, T, lk, BH, 128) ||
-            !make_tmap(&tvl, v_lo, false, TR::D, T, lv, BH, 128))
-            return IB200_ERR_CUDA;
-    } else {
-        tql = tq; tkl = tk; tvl = tv;
-    }
-    if (!cuda_ok(cudaFuncSetAttribute(attn_fwd_kernel<TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::SMEM_BYTES)))
-        return IB200_ERR_CUDA;
-    FwdParams prm;
-    prm.lse = lse;
-    prm.status = status;
-    prm.T = T;
-    prm.BH = static_cast<int>(BH);
-    prm.H = lq.H;
-    prm.causal = causal;
-    prm.scale_log2 = scale * 1.4426950408889634f;
-    const int pairs = (T + 255) / 256;
-    dim3 grid(pairs, static_cast<unsigned>(BH), 1);
-    IB200_SET_BOUNDS(TR::SPLIT ? 64 : TR::D, T, lq.H, static_cast<int>(BH / lq.H), static_cast<int>(BH), 0, TR::TM_COLS, status, stream);
-    record_timing_event(0, stream);
-    attn_fwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tql, tk, tkl, tv, tvl, to, prm);
-    const bool launched = cuda_ok(cudaGetLastError());
-    record_timing_event(1, stream);
-    return launched ? IB200_OK : IB200_ERR_CUDA;
-}
-
 // Number of head groups of a persistent kernel's item list (see locate_item).  The CTAs draw items in list order, so at
 // any time they work on a window of about one round (one item per CTA) of the list.  With every head in one group the window
 // would span up to one head per CTA, and the tiles the CTAs of a head share (K / V in the forward; Q / dO and the dQ
@@ -189,15 +150,24 @@ int persist_head_groups(int ctas, int items_per_head, long BH, size_t shared_byt
     return static_cast<int>(n_groups < 1 ? 1 : n_groups);
 }
 
-// bf16 operands: persistent CTAs walking (head, query-tile pair) items, heaviest first.
-template <int D>
-int launch_fwd_persist(const void* q, const void* k, const void* v, void* o, const RowLayout& lq, const RowLayout& lk, const RowLayout& lv,
-                       const RowLayout& lo, float* lse, int* status, long BH, int T, float scale, int causal, cudaStream_t stream) {
-    using TR = FwdPersistTraits<D>;
-    CUtensorMap tq, tk, tv, to;
+// Persistent CTAs walking (head, query-tile pair) items, heaviest first.  SPLIT: fp32 I/O, operands given as dense
+// (hi, lo) bf16 copies (q_lo, k_lo, v_lo), output fp32.
+template <int D, bool SPLIT>
+int launch_fwd_persist(const void* q, const void* q_lo, const void* k, const void* k_lo, const void* v, const void* v_lo, void* o,
+                       const RowLayout& lq, const RowLayout& lk, const RowLayout& lv, const RowLayout& lo, float* lse, int* status,
+                       long BH, int T, float scale, int causal, cudaStream_t stream) {
+    using TR = FwdPersistTraits<D, SPLIT>;
+    CUtensorMap tq, tql, tk, tkl, tv, tvl, to;
     if (!make_tmap(&tq, q, false, D, T, lq, BH, 128) || !make_tmap(&tk, k, false, D, T, lk, BH, 128) ||
-        !make_tmap(&tv, v, false, D, T, lv, BH, 128) || !make_tmap(&to, o, false, D, T, lo, BH, 128))
+        !make_tmap(&tv, v, false, D, T, lv, BH, 128) || !make_tmap(&to, o, SPLIT, D, T, lo, BH, 128))
         return IB200_ERR_CUDA;
+    if (SPLIT) {
+        if (!make_tmap(&tql, q_lo, false, D, T, lq, BH, 128) || !make_tmap(&tkl, k_lo, false, D, T, lk, BH, 128) ||
+            !make_tmap(&tvl, v_lo, false, D, T, lv, BH, 128))
+            return IB200_ERR_CUDA;
+    } else {
+        tql = tq; tkl = tk; tvl = tv;
+    }
     if (!cuda_ok(cudaFuncSetAttribute(attn_fwd_persist_kernel<TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::SMEM_BYTES)))
         return IB200_ERR_CUDA;
     FwdPersistParams pp;
@@ -215,22 +185,24 @@ int launch_fwd_persist(const void* q, const void* k, const void* v, void* o, con
     int dev = 0, sms = 148;
     if (cuda_ok(cudaGetDevice(&dev))) (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = static_cast<int>(items < sms ? items : sms);
-    pp.n_groups = persist_head_groups(sms, pp.pairs_per_head, BH, static_cast<size_t>(T) * D * 4 /*K, V*/);
-    pp.next_item = status + 1;              // second word of the workspace header, zeroed with it before every launch
+    pp.n_groups = persist_head_groups(sms, pp.pairs_per_head, BH, static_cast<size_t>(T) * D * (SPLIT ? 8 : 4) /*K, V*/);
+    pp.next_item = status + 1;              // second word of the workspace header, zeroed before every launch
     IB200_SET_BOUNDS(D, T, lq.H, static_cast<int>(BH / lq.H), static_cast<int>(BH), 0, TR::TM_COLS, status, stream);
     record_timing_event(0, stream);
-    attn_fwd_persist_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tk, tv, to, pp);
+    attn_fwd_persist_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tql, tk, tkl, tv, tvl, to, pp);
     const bool launched = cuda_ok(cudaGetLastError());
     record_timing_event(1, stream);
     return launched ? IB200_OK : IB200_ERR_CUDA;
 }
 
+// Persistent CTAs walking (head, key tile) items, longest walks first.  SPLIT (fp32 I/O): every operand is given as dense
+// (hi, lo) bf16 copies, index 0 / 1 of the pointer pairs; dK / dV come out as fp32.
 template <class TR>
-int launch_bwd(const void* const q[2], const void* const k[2], const void* const v[2], const void* const dO[2],
-               const RowLayout& lq, const RowLayout& lk, const RowLayout& lv, const RowLayout& ldo, const RowLayout& ldk,
-               const RowLayout& ldv, const float* nlse2, const float* ndelta, int T_pad, float* dq_acc, void* dk, void* dv, int* status, long BH, int T,
-               float scale, int causal, cudaStream_t stream) {
-    CUtensorMap tq[2], tk[2], tv[2], tdo[2], tdk, tdv;
+int launch_bwd_persist(const void* const q[2], const void* const k[2], const void* const v[2], const void* const dO[2],
+                       const RowLayout& lq, const RowLayout& lk, const RowLayout& lv, const RowLayout& ldo, const RowLayout& ldk,
+                       const RowLayout& ldv, const float* nlse2, const float* ndelta, int T_pad, float* dq_acc, void* dk, void* dv,
+                       int* status, long BH, int T, float scale, int causal, cudaStream_t stream) {
+    CUtensorMap tq[2], tk[2], tv[2], tdo[2], tdk, tdv, tdq;
     for (int i = 0; i < (TR::SPLIT ? 2 : 1); ++i) {
         if (!make_tmap(&tq[i], q[i], false, TR::D, T, lq, BH, TR::BQ) || !make_tmap(&tdo[i], dO[i], false, TR::D, T, ldo, BH, TR::BQ) ||
             !make_tmap(&tk[i], k[i], false, TR::D, T, lk, BH, TR::BKV) || !make_tmap(&tv[i], v[i], false, TR::D, T, lv, BH, TR::BKV))
@@ -238,51 +210,6 @@ int launch_bwd(const void* const q[2], const void* const k[2], const void* const
     }
     if (!TR::SPLIT) { tq[1] = tq[0]; tk[1] = tk[0]; tv[1] = tv[0]; tdo[1] = tdo[0]; }
     if (!make_tmap(&tdk, dk, TR::SPLIT, TR::D, T, ldk, BH, TR::BKV) || !make_tmap(&tdv, dv, TR::SPLIT, TR::D, T, ldv, BH, TR::BKV))
-        return IB200_ERR_CUDA;
-    // fp32 dQ accumulator, whole rows of D floats per box row, no swizzle (the staging tile is plain row-major)
-    CUtensorMap tdq;
-    {
-        EncodeTiledFn enc = encode_fn();
-        if (!enc) return IB200_ERR_CUDA;
-        cuuint64_t dims[3] = {static_cast<cuuint64_t>(TR::D), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(BH)};
-        cuuint64_t strides[2] = {static_cast<cuuint64_t>(TR::D) * 4, static_cast<cuuint64_t>(T) * TR::D * 4};
-        cuuint32_t box[3] = {static_cast<cuuint32_t>(TR::D), static_cast<cuuint32_t>(TR::BQ), 1};
-        cuuint32_t estr[3] = {1, 1, 1};
-        if (enc(&tdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, dq_acc, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return IB200_ERR_CUDA;
-    }
-    if (!cuda_ok(cudaFuncSetAttribute(attn_bwd_kernel<TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR::SMEM_BYTES)))
-        return IB200_ERR_CUDA;
-    BwdParams prm;
-    prm.nlse2 = nlse2;
-    prm.ndelta = ndelta;
-    prm.T_pad = T_pad;
-    prm.status = status;
-    prm.T = T;
-    prm.BH = static_cast<int>(BH);
-    prm.H = lq.H;
-    prm.causal = causal;
-    prm.scale = scale;
-    prm.scale_log2 = scale * 1.4426950408889634f;
-    dim3 grid((T + TR::BKV - 1) / TR::BKV, static_cast<unsigned>(BH), 1);
-    IB200_SET_BOUNDS(TR::D, T, lq.H, static_cast<int>(BH / lq.H), static_cast<int>(BH), 0, TR::TM_COLS, status, stream);
-    record_timing_event(2, stream);
-    attn_bwd_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq[0], tq[1], tk[0], tk[1], tv[0], tv[1], tdo[0], tdo[1], tdk, tdv, tdq, prm);
-    const bool launched = cuda_ok(cudaGetLastError());
-    record_timing_event(3, stream);
-    return launched ? IB200_OK : IB200_ERR_CUDA;
-}
-
-// bf16 operands: persistent CTAs walking (head, key tile) items, longest walks first.
-template <class TR>
-int launch_bwd_persist(const void* q, const void* k, const void* v, const void* dO, const RowLayout& lq, const RowLayout& lk, const RowLayout& lv,
-                       const RowLayout& ldo, const RowLayout& ldk, const RowLayout& ldv, const float* nlse2, const float* ndelta, int T_pad,
-                       float* dq_acc, void* dk, void* dv, int* status, long BH, int T, float scale, int causal, cudaStream_t stream) {
-    CUtensorMap tq, tk, tv, tdo, tdk, tdv, tdq;
-    if (!make_tmap(&tq, q, false, TR::D, T, lq, BH, TR::BQ) || !make_tmap(&tdo, dO, false, TR::D, T, ldo, BH, TR::BQ) ||
-        !make_tmap(&tk, k, false, TR::D, T, lk, BH, TR::BKV) || !make_tmap(&tv, v, false, TR::D, T, lv, BH, TR::BKV) ||
-        !make_tmap(&tdk, dk, false, TR::D, T, ldk, BH, TR::BKV) || !make_tmap(&tdv, dv, false, TR::D, T, ldv, BH, TR::BKV))
         return IB200_ERR_CUDA;
     {
         // fp32 dQ accumulator, whole rows of D floats per box row, no swizzle (the staging tile is plain row-major)
@@ -314,10 +241,12 @@ int launch_bwd_persist(const void* q, const void* k, const void* v, const void* 
     int dev = 0, sms = 148;
     if (cuda_ok(cudaGetDevice(&dev))) (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = static_cast<int>(items < sms ? items : sms);
-    const int n_groups = persist_head_groups(sms, (T + TR::BKV - 1) / TR::BKV, BH, static_cast<size_t>(T) * TR::D * 8 /*Q, dO, fp32 dQ*/);
+    const int n_groups = persist_head_groups(sms, (T + TR::BKV - 1) / TR::BKV, BH,
+                                             static_cast<size_t>(T) * TR::D * (TR::SPLIT ? 12 : 8) /*Q, dO (hi + lo), fp32 dQ*/);
     IB200_SET_BOUNDS(TR::D, T, lq.H, static_cast<int>(BH / lq.H), static_cast<int>(BH), 0, TR::TM_COLS, status, stream);
     record_timing_event(2, stream);
-    attn_bwd_persist_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdk, tdv, tdq, prm, static_cast<int>(items), n_groups,
+    attn_bwd_persist_kernel<TR><<<grid, TR::THREADS, TR::SMEM_BYTES, stream>>>(tq[0], tq[1], tk[0], tk[1], tv[0], tv[1], tdo[0], tdo[1], tdk, tdv, tdq, prm,
+                                                                               static_cast<int>(items), n_groups,
                                                                                status + 1 /*draw counter: header word zeroed before every launch*/);
     const bool launched = cuda_ok(cudaGetLastError());
     record_timing_event(3, stream);
@@ -328,11 +257,12 @@ struct BwdLayouts {
     RowLayout q, k, v, o, dO, dq, dk, dv;
 };
 
-// delta pre-pass -> main kernel -> dQ finish.
+// pre-pass (delta, accumulator zeroing, header, fp32 operand splits) -> main kernel -> dQ finish.
 // Workspace: [header | dq accumulator | -delta, -lse*log2e | (fp32 only) dense hi/lo bf16 copies of q, k, v, dO].
-int launch_bwd_all(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
-                   void* dq, void* dk, void* dv, const BwdLayouts& L, long BH, int T, int D, float scale, int causal, bool f32,
-                   uint8_t* ws, cudaStream_t stream) {
+template <int D, bool F32>
+int launch_bwd_typed(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
+                     void* dq, void* dk, void* dv, const BwdLayouts& L, long BH, int T, float scale, int causal,
+                     uint8_t* ws, cudaStream_t stream) {
     const long N = BH * T * D;
     int* status = reinterpret_cast<int*>(ws);
     float* dq_acc = reinterpret_cast<float*>(ws + kHeaderBytes);
@@ -341,40 +271,45 @@ int launch_bwd_all(const void* q, const void* k, const void* v, const void* o, c
     const size_t vec_bytes = round_up(static_cast<size_t>(BH) * T_pad * 4, 256);
     float* ndelta = reinterpret_cast<float*>(after_acc);
     float* nlse2 = reinterpret_cast<float*>(after_acc + vec_bytes);
-    int rc = prepare_header(ws, stream);
-    if (rc) return rc;
-    if (!cuda_ok(cudaMemsetAsync(dq_acc, 0, round_up(N * 4, 256), stream))) return IB200_ERR_CUDA;
-    if (f32) {
+    BwdPrepassJob job;
+    job.o = o; job.dO = dO; job.lse = lse; job.ndelta = ndelta; job.nlse2 = nlse2;
+    job.lo = L.o; job.ldo = L.dO;
+    job.dq_acc = reinterpret_cast<float4*>(dq_acc);
+    job.header = status;
+    const void* qp[2] = {q, q}; const void* kp[2] = {k, k}; const void* vp[2] = {v, v}; const void* dop[2] = {dO, dO};
+    RowLayout lq = L.q, lk = L.k, lv = L.v, ldo = L.dO;
+    if (F32) {
         uint8_t* base = after_acc + 2 * vec_bytes;
         const size_t slab = round_up(N * 2, 256);
-        const void* part[8];
+        const void** dst[4] = {qp, kp, vp, dop};
         const float* src[4] = {static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v), static_cast<const float*>(dO)};
         const RowLayout* lsrc[4] = {&L.q, &L.k, &L.v, &L.dO};
         for (int i = 0; i < 4; ++i) {
-            part[2 * i] = base + (2 * i) * slab;
-            part[2 * i + 1] = base + (2 * i + 1) * slab;
-            rc = launch_split_bf16(src[i], const_cast<void*>(part[2 * i]), const_cast<void*>(part[2 * i + 1]), *lsrc[i], BH, T, D, stream);
-            if (rc) return rc;
+            job.split.in[i] = src[i];
+            job.split.hi[i] = reinterpret_cast<uint4*>(base + (2 * i) * slab);
+            job.split.lo[i] = reinterpret_cast<uint4*>(base + (2 * i + 1) * slab);
+            job.split.lin[i] = *lsrc[i];
+            dst[i][0] = job.split.hi[i];
+            dst[i][1] = job.split.lo[i];
         }
-        const RowLayout dl = dense_layout(L.q.H, T, D);      // the hi/lo copies are dense
-        rc = launch_delta<64, true>(o, dO, lse, ndelta, nlse2, L.o, L.dO, BH, T, T_pad, stream); if (rc) return rc;
-        rc = launch_bwd<BwdTraits<64, true>>(&part[0], &part[2], &part[4], &part[6], dl, dl, dl, dl, L.dk, L.dv, nlse2, ndelta, T_pad,
-                                             dq_acc, dk, dv, status, BH, T, scale, causal, stream);
-        if (rc) return rc;
-        return launch_dq_finish<64, true>(dq_acc, dq, scale, L.dq, BH, T, stream);
-    }
-    if (D == 64) {
-        rc = launch_delta<64, false>(o, dO, lse, ndelta, nlse2, L.o, L.dO, BH, T, T_pad, stream); if (rc) return rc;
-        rc = launch_bwd_persist<BwdTraits<64, false>>(q, k, v, dO, L.q, L.k, L.v, L.dO, L.dk, L.dv, nlse2, ndelta, T_pad, dq_acc, dk, dv, status,
-                                                      BH, T, scale, causal, stream);
+        lq = lk = lv = ldo = dense_layout(L.q.H, T, D);      // the hi/lo copies are dense
     } else {
-        rc = launch_delta<128, false>(o, dO, lse, ndelta, nlse2, L.o, L.dO, BH, T, T_pad, stream); if (rc) return rc;
-        rc = launch_bwd_persist<BwdTraits<128, false>>(q, k, v, dO, L.q, L.k, L.v, L.dO, L.dk, L.dv, nlse2, ndelta, T_pad, dq_acc, dk, dv, status,
-                                                       BH, T, scale, causal, stream);
+        for (int i = 0; i < 4; ++i) { job.split.in[i] = nullptr; job.split.hi[i] = job.split.lo[i] = nullptr; job.split.lin[i] = L.q; }
     }
+    int rc = launch_bwd_prepass<D, F32>(job, BH, T, T_pad, stream);
     if (rc) return rc;
-    return D == 64 ? launch_dq_finish<64, false>(dq_acc, dq, scale, L.dq, BH, T, stream)
-                   : launch_dq_finish<128, false>(dq_acc, dq, scale, L.dq, BH, T, stream);
+    rc = launch_bwd_persist<BwdTraits<D, F32>>(qp, kp, vp, dop, lq, lk, lv, ldo, L.dk, L.dv, nlse2, ndelta, T_pad, dq_acc, dk, dv, status,
+                                               BH, T, scale, causal, stream);
+    if (rc) return rc;
+    return launch_dq_finish<D, F32>(dq_acc, dq, scale, L.dq, BH, T, stream);
+}
+
+int launch_bwd_all(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
+                   void* dq, void* dk, void* dv, const BwdLayouts& L, long BH, int T, int D, float scale, int causal, bool f32,
+                   uint8_t* ws, cudaStream_t stream) {
+    if (f32) return launch_bwd_typed<64, true>(q, k, v, o, dO, lse, dq, dk, dv, L, BH, T, scale, causal, ws, stream);
+    if (D == 64) return launch_bwd_typed<64, false>(q, k, v, o, dO, lse, dq, dk, dv, L, BH, T, scale, causal, ws, stream);
+    return launch_bwd_typed<128, false>(q, k, v, o, dO, lse, dq, dk, dv, L, BH, T, scale, causal, ws, stream);
 }
 
 // A caller-supplied layout (NULL = dense), checked: rows of D elements must start on 16-byte boundaries.
@@ -512,22 +447,31 @@ int fwd_core(const void* q, const void* k, const void* v, void* o, float* lse, c
 
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     int* status = reinterpret_cast<int*>(ws);
-    if ((rc = prepare_header(ws, stream))) return rc;
+    if (!f32 && (rc = prepare_header(ws, stream))) return rc;      // fp32 I/O: the split pre-pass prepares the header
     if (f32) {
         // fp32 operands are carried as dense (hi, lo) bf16 pairs
         const size_t slab = round_up(N * 2, 256);
         uint8_t* base = ws + kHeaderBytes;
         void* part[6];
         for (int i = 0; i < 6; ++i) part[i] = base + i * slab;
-        rc = launch_split_bf16(static_cast<const float*>(q), part[0], part[1], lq, BH, T, D, stream); if (rc) return rc;
-        rc = launch_split_bf16(static_cast<const float*>(k), part[2], part[3], lk, BH, T, D, stream); if (rc) return rc;
-        rc = launch_split_bf16(static_cast<const float*>(v), part[4], part[5], lv, BH, T, D, stream); if (rc) return rc;
+        SplitJob job;
+        const float* src[3] = {static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v)};
+        const RowLayout* lsrc[3] = {&lq, &lk, &lv};
+        for (int i = 0; i < 3; ++i) {
+            job.in[i] = src[i];
+            job.hi[i] = static_cast<uint4*>(part[2 * i]);
+            job.lo[i] = static_cast<uint4*>(part[2 * i + 1]);
+            job.lin[i] = *lsrc[i];
+        }
+        job.in[3] = nullptr; job.hi[3] = job.lo[3] = nullptr; job.lin[3] = lq;
+        rc = launch_split_bf16(job, 3, status, BH, T, D, stream);
+        if (rc) return rc;
         const RowLayout dl = dense_layout(H, T, D);
-        return launch_fwd<FwdTraits<64, true>>(part[0], part[1], part[2], part[3], part[4], part[5], o, dl, dl, dl, lo, lse, status, BH, T,
-                                               scale, causal, stream);
+        return launch_fwd_persist<64, true>(part[0], part[1], part[2], part[3], part[4], part[5], o, dl, dl, dl, lo, lse, status, BH, T,
+                                            scale, causal, stream);
     }
-    if (D == 64) return launch_fwd_persist<64>(q, k, v, o, lq, lk, lv, lo, lse, status, BH, T, scale, causal, stream);
-    return launch_fwd_persist<128>(q, k, v, o, lq, lk, lv, lo, lse, status, BH, T, scale, causal, stream);
+    if (D == 64) return launch_fwd_persist<64, false>(q, nullptr, k, nullptr, v, nullptr, o, lq, lk, lv, lo, lse, status, BH, T, scale, causal, stream);
+    return launch_fwd_persist<128, false>(q, nullptr, k, nullptr, v, nullptr, o, lq, lk, lv, lo, lse, status, BH, T, scale, causal, stream);
 }
 
 int bwd_core(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse, void* dq, void* dk, void* dv,

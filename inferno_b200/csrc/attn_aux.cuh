@@ -1,7 +1,9 @@
 // Bandwidth-bound helper kernels around the attention main kernels:
 //   * split_bf16   fp32 x -> (hi, lo) bf16 pair with hi = bf16(x), lo = bf16(x - hi); the
 //                  fp32-I/O kernels multiply such pairs in three bf16 MMAs
-//   * delta        -delta[row] = -sum_d O[row,d] * dO[row,d] (and -lse*log2e beside it); this is the reference's
+//   * bwd_prepass  one launch ahead of the backward main kernel: -delta[row] = -sum_d O[row,d] * dO[row,d] (and
+//                  -lse*log2e beside it), the zeroing of the dQ accumulator, the workspace header and (fp32 I/O) the
+//                  operand splits; delta is the reference's
 //                  dot = sum_j dP_ij P_ij (src/inferno/gradfn/softmaxbackward.h:101-109)
 //                  rewritten so that it needs no [T,T] matrix
 //   * dq_finish    dQ = scale * accumulator, cast to the output type; the scale is
@@ -42,16 +44,24 @@ constexpr int kAuxThreads = 256;
 constexpr int kAuxBlocks = 148 * 8;
 
 // hi = bf16(x), lo = bf16(x - hi): 8 elements per thread, two 16-byte loads, two 16-byte stores.
-// Reads rows through `lin` (any layout) and writes hi / lo dense, so the main kernels always see dense
-// operand copies in fp32-I/O mode.
-__global__ void __launch_bounds__(kAuxThreads) split_bf16_kernel(const float* __restrict__ in, uint4* __restrict__ hi, uint4* __restrict__ lo,
-                                                                 RowLayout lin, int T, int D) {
+// Reads rows through the operand's layout (any layout) and writes hi / lo dense, so the main kernels always see dense
+// operand copies in fp32-I/O mode.  One launch splits every operand of a pass (q, k, v forward; q, k, v, dO backward):
+// grid z selects the operand, grid y the head.
+struct SplitJob {
+    const float* in[4];
+    uint4* hi[4];
+    uint4* lo[4];
+    RowLayout lin[4];
+};
+__device__ __forceinline__ void split_bf16_block(const SplitJob& job, int z, int T, int D) {
+    const float* __restrict__ in = job.in[z];
+    const RowLayout lin = job.lin[z];
     const int cpr = D / 8;                                   // 8-element chunks per row
     const long head = blockIdx.y;                            // one head per grid row
     const long base_in = lin.row(head, 0);
     const int n8 = T * cpr;
-    uint4* hi_h = hi + head * static_cast<long>(n8);
-    uint4* lo_h = lo + head * static_cast<long>(n8);
+    uint4* __restrict__ hi_h = job.hi[z] + head * static_cast<long>(n8);
+    uint4* __restrict__ lo_h = job.lo[z] + head * static_cast<long>(n8);
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += gridDim.x * blockDim.x) {
         const int t = i / cpr, c8 = i - t * cpr;
         const float4* src = reinterpret_cast<const float4*>(in + base_in + static_cast<long>(t) * lin.st + c8 * 8);
@@ -71,12 +81,27 @@ __global__ void __launch_bounds__(kAuxThreads) split_bf16_kernel(const float* __
     }
 }
 
-inline int launch_split_bf16(const float* in, void* hi, void* lo, const RowLayout& lin, long heads, int T, int D, cudaStream_t stream) {
+// Workspace header (see attn_api.cu): word 0 = sticky device status, word 1 = draw counter of the persistent kernels
+// (zero at every launch), word 3 = "status word is valid" mark for a workspace that arrives uninitialised.
+constexpr int kHeaderMagic = 0x1b200a77;
+__device__ __forceinline__ void prepare_header(int* hdr) {
+    if (hdr[3] != kHeaderMagic) { hdr[0] = 0; hdr[3] = kHeaderMagic; }
+    hdr[1] = 0;
+}
+
+// Forward pre-pass of the fp32-I/O path: q, k, v -> hi / lo copies (grid z = operand), and the header.
+__global__ void __launch_bounds__(kAuxThreads) split_bf16_kernel(SplitJob job, int* header, int T, int D) {
+    if (header && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) prepare_header(header);
+    split_bf16_block(job, blockIdx.z, T, D);
+}
+
+// n_ops operands (3 or 4) in one launch.
+inline int launch_split_bf16(const SplitJob& job, int n_ops, int* header, long heads, int T, int D, cudaStream_t stream) {
     const int n8 = T * (D / 8);
     int bx = (n8 + kAuxThreads - 1) / kAuxThreads;
     if (bx > 64) bx = 64;                                    // grid-stride inside a head beyond that
-    dim3 grid(bx, static_cast<unsigned>(heads), 1);
-    split_bf16_kernel<<<grid, kAuxThreads, 0, stream>>>(in, reinterpret_cast<uint4*>(hi), reinterpret_cast<uint4*>(lo), lin, T, D);
+    dim3 grid(bx, static_cast<unsigned>(heads), static_cast<unsigned>(n_ops));
+    split_bf16_kernel<<<grid, kAuxThreads, 0, stream>>>(job, header, T, D);
     return launch_status();
 }
 
@@ -107,9 +132,9 @@ __global__ void __launch_bounds__(kAuxThreads) cast_bf16_f32_kernel(const uint4*
 //   ndelta[h, t] = -sum_d O[h,t,d] * dO[h,t,d]        nlse2[h, t] = -lse[h,t] * log2(e)
 // Padding rows (t >= T) are written as 0.
 template <int D, bool F32>
-__global__ void __launch_bounds__(kAuxThreads) delta_kernel(const void* __restrict__ o_, const void* __restrict__ do_, const float* __restrict__ lse,
-                                                            float* __restrict__ ndelta, float* __restrict__ nlse2, RowLayout lo, RowLayout ldo,
-                                                            int T, int T_pad) {
+__device__ __forceinline__ void delta_block(const void* __restrict__ o_, const void* __restrict__ do_, const float* __restrict__ lse,
+                                            float* __restrict__ ndelta, float* __restrict__ nlse2, const RowLayout& lo, const RowLayout& ldo,
+                                            int T, int T_pad) {
     constexpr int EPT = F32 ? 4 : 8;              // elements per 16-byte load
     constexpr int TPR = D / EPT;                  // threads per row (8 or 16)
     constexpr int RPB = kAuxThreads / TPR;        // rows per block per step
@@ -163,12 +188,43 @@ __global__ void __launch_bounds__(kAuxThreads) delta_kernel(const void* __restri
     }
 }
 
+// The backward's one pre-pass launch.  Grid y = head; grid z selects the job:
+//   z = 0      -delta and -lse*log2e of the head's rows (delta_block), and the workspace header
+//   z = 1      zeroes the head's slice of the fp32 dQ accumulator (the main kernel adds into it)
+//   z = 2..5   (fp32 I/O only) q, k, v, dO -> hi / lo bf16 copies
+// grid x = blocks of 64 rows, which is what delta_block needs; the other jobs stride over it.
+struct BwdPrepassJob {
+    const void* o;
+    const void* dO;
+    const float* lse;
+    float* ndelta;
+    float* nlse2;
+    RowLayout lo, ldo;
+    float4* dq_acc;        // dense [heads, T, D] fp32
+    int* header;
+    SplitJob split;        // used when F32
+};
 template <int D, bool F32>
-inline int launch_delta(const void* o, const void* dO, const float* lse, float* ndelta, float* nlse2, const RowLayout& lo,
-                        const RowLayout& ldo, long heads, int T, int T_pad, cudaStream_t stream) {
+__global__ void __launch_bounds__(kAuxThreads) bwd_prepass_kernel(BwdPrepassJob job, int T, int T_pad) {
+    const int z = blockIdx.z;
+    if (z == 0) {
+        if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) prepare_header(job.header);
+        delta_block<D, F32>(job.o, job.dO, job.lse, job.ndelta, job.nlse2, job.lo, job.ldo, T, T_pad);
+    } else if (z == 1) {
+        const long n4 = static_cast<long>(T) * (D / 4);                      // float4 chunks of this head's accumulator slice
+        float4* dst = job.dq_acc + static_cast<long>(blockIdx.y) * n4;
+        for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n4; i += static_cast<long>(gridDim.x) * blockDim.x)
+            dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    } else if constexpr (F32) {
+        split_bf16_block(job.split, z - 2, T, D);
+    }
+}
+
+template <int D, bool F32>
+inline int launch_bwd_prepass(const BwdPrepassJob& job, long heads, int T, int T_pad, cudaStream_t stream) {
     constexpr int RPB = kAuxThreads / (D / (F32 ? 4 : 8));
-    dim3 grid((T_pad + RPB * 4 - 1) / (RPB * 4), static_cast<unsigned>(heads), 1);
-    delta_kernel<D, F32><<<grid, kAuxThreads, 0, stream>>>(o, dO, lse, ndelta, nlse2, lo, ldo, T, T_pad);
+    dim3 grid((T_pad + RPB * 4 - 1) / (RPB * 4), static_cast<unsigned>(heads), F32 ? 6 : 2);
+    bwd_prepass_kernel<D, F32><<<grid, kAuxThreads, 0, stream>>>(job, T, T_pad);
     return launch_status();
 }
 

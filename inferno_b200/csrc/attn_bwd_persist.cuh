@@ -1,9 +1,8 @@
-// Causal flash-attention backward for sm_100a, bf16 operands: persistent CTAs.
+// Causal flash-attention backward for sm_100a: persistent CTAs (bf16 operands, and fp32 I/O carried as hi/lo bf16 pairs).
 //
-// Same block algorithm, warp roles, shared-memory and TMEM plan as attn_bwd_kernel (attn_bwd.cuh, which names the
-// reference nodes the backward replaces).  One CTA per SM walks a list of work items (one item = one 128-row key / value
-// tile of one head), and all mbarrier phases run on from item to item (each role
-// counts the query blocks it has handled), so that
+// Block algorithm, warp roles, shared-memory and TMEM plan: attn_bwd.cuh (which names the reference nodes the backward
+// replaces).  One CTA per SM walks a list of work items (one item = one 128-row key / value tile of one head), and all
+// mbarrier phases run on from item to item (each role counts the query blocks it has handled), so that
 //   * the TMA warp loads the next item's K and V tiles as soon as the last MMA of the current item has completed, and
 //     keeps the Q / dO ring running straight into the next item;
 //   * the four drain warps, not the compute warps, turn dK / dV into bf16 (staged in their own dQ^T staging tile, which
@@ -11,7 +10,8 @@
 //     blocks and the MMA warp to its S^T / dP^T / dQ^T; only an item's first dK / dV MMAs wait until the drain warps have
 //     read the accumulators out of TMEM;
 //   * a CTA's launch, barrier set-up, TMEM allocation and tear-down are paid once per SM instead of once per item.
-// A non-persistent CTA spends about 11 us outside its steady state (17 % of an average item at T = 4096).
+// A CTA launched per item spends about 11 us outside its steady state (17 % of an average item at T = 4096; measured
+// on the one-CTA-per-item form this kernel replaced).
 // Items are drawn, not assigned: a CTA starts on item blockIdx.x and its TMA thread draws every further index from a
 // counter in global memory (ItemRing in sm100_ptx.cuh hands it to the other roles).  The list runs over groups of
 // consecutive heads (locate_item) so that the CTAs share the Q / dO tiles and the fp32 dQ accumulator of few heads in L2 at
@@ -24,21 +24,26 @@ namespace ib200 {
 
 template <class TR>
 __global__ void __launch_bounds__(TR::THREADS, 1)
-attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_q_lo,
+                        const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_k_lo,
+                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_v_lo,
+                        const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_do_lo,
                         const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
                         const __grid_constant__ CUtensorMap tm_dq, BwdParams prm, int n_items, int n_groups, int* next_item) {
-    static_assert(!TR::SPLIT, "bf16 operands only");
     constexpr int D = TR::D, BKV = TR::BKV, BQ = TR::BQ, NS = TR::NS;
+    constexpr bool SPLIT = TR::SPLIT;
     // groups of four queries (of the eight a compute thread handles per block) whose lse / delta values are fetched early;
     // measured on one GPU with the builds swapped in place: at D = 128 all 8 (+2 % at T >= 4096 over 6, -2.5 % at T = 1024), at
     // D = 64 4 (6 and 8 cost 3-12 %: the variant starts to spill)
-    constexpr int kPre = (D == 128) ? 8 : 4;
+    // (split mode: none -- its compute threads carry twice the packed values, and early loads made them spill)
+    constexpr int kPre = SPLIT ? 0 : (D == 128) ? 8 : 4;
+    constexpr int kPreN = kPre > 0 ? kPre : 1;
     // D = 128: wait for the dS^T tile before phase two instead of just before the stores (+0.5-1 %; -3 % at D = 64)
     constexpr bool kWaitDsEarly = (D == 128);
     // D = 64: S^T is handed to the compute warps before dP^T has been issued, so that their exponentials run under it (+8 %);
     // at D = 128, where the MMA side paces the block, the extra commit and wait bought nothing and one hand-off is used
-    constexpr bool kSplitHandoff = (D == 64);
+    // (split mode triples the MMA work per block, so there too the MMA side paces and one hand-off is used)
+    constexpr bool kSplitHandoff = (D == 64) && !SPLIT;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* sK = smem + TR::OFF_K;
@@ -99,6 +104,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     if (warp == 12 && lane == 0) {
         tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_do);
         tma_prefetch_desc(&tm_dk); tma_prefetch_desc(&tm_dv); tma_prefetch_desc(&tm_dq);
+        if constexpr (SPLIT) { tma_prefetch_desc(&tm_q_lo); tma_prefetch_desc(&tm_k_lo); tma_prefetch_desc(&tm_v_lo); tma_prefetch_desc(&tm_do_lo); }
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -123,9 +129,11 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 const int drawn = atomicAdd(next_item, 1);
                 if (ni > 0) mbar_wait(dkv_full, (ni - 1) & 1, ab, 12);          // the previous item's MMAs have finished with K, V
                 mbar_arrive_expect_tx(kv_full, 2 * TR::KV_TILE);
+                // panel p of a tile: columns 64p.. of a bf16 operand, or (fp32 I/O) the hi / lo half of the bf16 pair
+                auto col = [](int p) { return SPLIT ? 0 : p * 64; };
                 for (int p = 0; p < TR::NP; ++p) {
-                    tma_load_4d(sK + p * TR::KV_PANEL, &tm_k, kv_full, p * 64, item.n * BKV, item.hd, item.bt);
-                    tma_load_4d(sV + p * TR::KV_PANEL, &tm_v, kv_full, p * 64, item.n * BKV, item.hd, item.bt);
+                    tma_load_4d(sK + p * TR::KV_PANEL, (SPLIT && p) ? &tm_k_lo : &tm_k, kv_full, col(p), item.n * BKV, item.hd, item.bt);
+                    tma_load_4d(sV + p * TR::KV_PANEL, (SPLIT && p) ? &tm_v_lo : &tm_v, kv_full, col(p), item.n * BKV, item.hd, item.bt);
                 }
                 idx = static_cast<int>(gridDim.x) + drawn;
                 item_ring_publish(items, ni, idx, ab);
@@ -135,8 +143,8 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                     mbar_wait(&qdo_empty[s], ((g / NS) & 1) ^ 1, ab, 10);
                     mbar_arrive_expect_tx(&qdo_full[s], 2 * TR::Q_TILE + 2 * BQ * 4);
                     for (int p = 0; p < TR::NP; ++p) {
-                        tma_load_4d(sQ + s * TR::Q_TILE + p * TR::Q_PANEL, &tm_q, &qdo_full[s], p * 64, m * BQ, item.hd, item.bt);
-                        tma_load_4d(sDO + s * TR::Q_TILE + p * TR::Q_PANEL, &tm_do, &qdo_full[s], p * 64, m * BQ, item.hd, item.bt);
+                        tma_load_4d(sQ + s * TR::Q_TILE + p * TR::Q_PANEL, (SPLIT && p) ? &tm_q_lo : &tm_q, &qdo_full[s], col(p), m * BQ, item.hd, item.bt);
+                        tma_load_4d(sDO + s * TR::Q_TILE + p * TR::Q_PANEL, (SPLIT && p) ? &tm_do_lo : &tm_do, &qdo_full[s], col(p), m * BQ, item.hd, item.bt);
                     }
                     // the block's 64 values of -lse*log2e and of -delta (padded rows, so always aligned and in range)
                     const size_t voff = static_cast<size_t>(item.bh) * prm.T_pad + static_cast<size_t>(m) * BQ;
@@ -181,12 +189,22 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 const uint32_t t_st = tmem + TR::TM_ST + b * 64, t_dp = tmem + TR::TM_DP + b * 64;
                 mbar_wait(&pds_full[b], (gb >> 1) & 1, ab, 22);
                 tc_fence_after_sync();
-                bwd_issue_dq<TR>(t_dp, lK_mn, lDS, leader);                            // dQ^T over the consumed dP^T buffer
-                if (leader) umma_commit(&dq_full[b]);
-                // the item's first dK / dV MMAs overwrite the accumulators: the previous epilogue must have read them
-                if (it == 0 && ni > 0) { mbar_wait(dkv_free, (ni - 1) & 1, ab, 26); tc_fence_after_sync(); }
-                bwd_issue_acc<TR>(tmem + TR::TM_DK, t_st, 1, lQ_mn, it > 0, leader);   // dK += dS^T Q
-                bwd_issue_acc<TR>(tmem + TR::TM_DV, t_st, 0, lDO_mn, it > 0, leader);  // dV += P^T dO
+                if constexpr (!SPLIT) {
+                    bwd_issue_dq<TR>(t_dp, lK_mn, lDS, leader);                            // dQ^T over the consumed dP^T buffer
+                    if (leader) umma_commit(&dq_full[b]);
+                    // the item's first dK / dV MMAs overwrite the accumulators: the previous epilogue must have read them
+                    if (it == 0 && ni > 0) { mbar_wait(dkv_free, (ni - 1) & 1, ab, 26); tc_fence_after_sync(); }
+                    bwd_issue_acc<TR>(tmem + TR::TM_DK, t_st, 1, lQ_mn, it > 0, leader);   // dK += dS^T Q
+                    bwd_issue_acc<TR>(tmem + TR::TM_DV, t_st, 0, lDO_mn, it > 0, leader);  // dV += P^T dO
+                } else {
+                    // split mode: {P^T hi, lo} live in the S^T buffer and {dS^T hi, lo} in the dP^T buffer, so dK reads the
+                    // latter before dQ^T overwrites it
+                    if (it == 0 && ni > 0) { mbar_wait(dkv_free, (ni - 1) & 1, ab, 26); tc_fence_after_sync(); }
+                    bwd_issue_acc<TR>(tmem + TR::TM_DV, t_st, 0, lDO_mn, it > 0, leader);
+                    bwd_issue_acc<TR>(tmem + TR::TM_DK, t_dp, 0, lQ_mn, it > 0, leader);
+                    bwd_issue_dq<TR>(t_dp, lK_mn, lDS, leader);
+                    if (leader) umma_commit(&dq_full[b]);
+                }
                 if (leader) umma_commit(&qdo_empty[s]);
                 if (it + 2 < nblk) issue_front(gb + 2);
             }
@@ -222,7 +240,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 // the block's -lse*log2e and -delta values (kPre groups of four queries) now, under the wait for S^T / dP^T: with
                 // the MMA operand reads loading the shared-memory pipe these broadcast loads take a few hundred cycles when
                 // issued in the element loop
-                float4 nl_pre[kPre], nd_pre[kPre];
+                float4 nl_pre[kPreN], nd_pre[kPreN];
 #pragma unroll
                 for (int e4 = 0; e4 < kPre; ++e4) {
                     nl_pre[e4] = reinterpret_cast<const float4*>(v_lse)[e4];
@@ -236,7 +254,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 const bool diag = prm.causal && (m * BQ < (n + 1) * BKV);
                 const int q0 = m * BQ + h * 32;
                 const bool masked = diag || tail_tile;             // uniform per block: most blocks take the unmasked path
-                uint32_t pk[16], dk[16];
+                uint32_t pk[16], dk[16], pl[16], dl[16];       // (hi, lo) bf16 pairs; the lo halves only in split mode
                 const uint64_t c2 = pack_f32x2(c, c);
                 const float4* v_lse4 = reinterpret_cast<const float4*>(v_lse);
                 const float4* v_del4 = reinterpret_cast<const float4*>(v_del);
@@ -262,11 +280,14 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                             sr[e] = __float_as_uint(p0);
                             sr[e + 1] = __float_as_uint(p1);
                             pk[e >> 1] = pack_bf16x2(p0, p1);
+                            if constexpr (SPLIT)
+                                pl[e >> 1] = pack_bf16x2(p0 - __uint_as_float(pk[e >> 1] << 16), p1 - __uint_as_float(pk[e >> 1] & 0xffff0000u));
                         }
                     }
                 };
                 if (masked) body_p(MaskedTag<true>{}); else body_p(MaskedTag<false>{});
                 tmem_st_x16(t_st, pk);
+                if constexpr (SPLIT) tmem_st_x16(t_st + 16, pl);
                 // Phase two, once dP^T is there: dS^T = P^T o (dP^T - delta).
                 // The single dS^T shared-memory tile is free once dQ^T of the previous block (of this or the previous item) has
                 // completed (a second tile, which would fit exactly, was measured: no gain); at D = 128 that wait comes first.
@@ -288,13 +309,23 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                         float d0, d1;
                         unpack_f32x2(fmul2(p2, fadd2(pack_f32x2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])), nd2)), d0, d1);
                         dk[e >> 1] = pack_bf16x2(d0, d1);
+                        if constexpr (SPLIT)
+                            dl[e >> 1] = pack_bf16x2(d0 - __uint_as_float(dk[e >> 1] << 16), d1 - __uint_as_float(dk[e >> 1] & 0xffff0000u));
                     }
                 }
-                tmem_st_x16(t_st + 16, dk);
+                if constexpr (!SPLIT) {
+                    tmem_st_x16(t_st + 16, dk);
+                } else {
+                    tmem_st_x16(t_dp, dk);          // dP^T has been read into registers: its buffer takes {dS^T hi, lo}
+                    tmem_st_x16(t_dp + 16, dl);
+                }
                 if (!kWaitDsEarly && gb >= 1) mbar_wait(&dq_full[(gb - 1) & 1], ((gb - 1) >> 1) & 1, ab, 32);
 #pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4)
+                for (int c4 = 0; c4 < 4; ++c4) {
                     st_shared_sw128(sDS, r, h * 4 + c4, make_uint4(dk[4 * c4], dk[4 * c4 + 1], dk[4 * c4 + 2], dk[4 * c4 + 3]));
+                    if constexpr (SPLIT)
+                        st_shared_sw128(sDS + TR::DS_PART, r, h * 4 + c4, make_uint4(dl[4 * c4], dl[4 * c4 + 1], dl[4 * c4 + 2], dl[4 * c4 + 3]));
+                }
                 tmem_wait_st();
                 fence_proxy_async_smem();
                 tc_fence_before_sync();
@@ -369,15 +400,28 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                         __syncwarp();
                         if (lane == 0) mbar_arrive(dkv_free);
                     }
-                    const int panel = cc / 64, chunk0 = (cc % 64) / 8;
+                    if constexpr (!SPLIT) {
+                        const int panel = cc / 64, chunk0 = (cc % 64) / 8;
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint4 v;
-                        v.x = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 0]) * mul, __uint_as_float(rr[q4 * 8 + 1]) * mul);
-                        v.y = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 2]) * mul, __uint_as_float(rr[q4 * 8 + 3]) * mul);
-                        v.z = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 4]) * mul, __uint_as_float(rr[q4 * 8 + 5]) * mul);
-                        v.w = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 6]) * mul, __uint_as_float(rr[q4 * 8 + 7]) * mul);
-                        st_shared_sw128(stage_b + panel * TR::KV_PANEL, r, chunk0 + q4, v);
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            uint4 v;
+                            v.x = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 0]) * mul, __uint_as_float(rr[q4 * 8 + 1]) * mul);
+                            v.y = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 2]) * mul, __uint_as_float(rr[q4 * 8 + 3]) * mul);
+                            v.z = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 4]) * mul, __uint_as_float(rr[q4 * 8 + 5]) * mul);
+                            v.w = pack_bf16x2(__uint_as_float(rr[q4 * 8 + 6]) * mul, __uint_as_float(rr[q4 * 8 + 7]) * mul);
+                            st_shared_sw128(stage_b + panel * TR::KV_PANEL, r, chunk0 + q4, v);
+                        }
+                    } else {
+                        const int panel = cc / 32;     // 32 fp32 columns = one 128-byte panel row
+#pragma unroll
+                        for (int q4 = 0; q4 < 8; ++q4) {
+                            uint4 v;
+                            v.x = __float_as_uint(__uint_as_float(rr[q4 * 4 + 0]) * mul);
+                            v.y = __float_as_uint(__uint_as_float(rr[q4 * 4 + 1]) * mul);
+                            v.z = __float_as_uint(__uint_as_float(rr[q4 * 4 + 2]) * mul);
+                            v.w = __float_as_uint(__uint_as_float(rr[q4 * 4 + 3]) * mul);
+                            st_shared_sw128(stage_b + panel * TR::KV_PANEL, r, q4, v);
+                        }
                     }
                 }
                 fence_proxy_async_smem();

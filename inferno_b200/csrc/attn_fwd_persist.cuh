@@ -1,16 +1,16 @@
-// Causal flash-attention forward for sm_100a, bf16 operands: persistent CTAs.
+// Causal flash-attention forward for sm_100a: persistent CTAs (bf16 operands, and fp32 I/O carried as hi/lo bf16 pairs).
 //
-// Same tile algorithm, warp roles and TMEM plan as attn_fwd_kernel (attn_fwd.cuh, which names the reference code the
-// forward replaces: InfernoApp/main.cpp:737-754).  The difference is the outer structure: one CTA per SM walks a list of
-// work items (one item = two adjacent 128-row query tiles of one head), and the roles run ahead of
-// each other across item boundaries:
+// Tile algorithm, warp roles and TMEM plan: attn_fwd.cuh (which names the reference code the forward replaces:
+// InfernoApp/main.cpp:737-754).  Outer structure: one CTA per SM walks a list of work items (one item = two adjacent
+// 128-row query tiles of one head), and the roles run ahead of each other across item boundaries:
 //   * the TMA warp loads the next item's Q tiles and first K tile as soon as the last S = Q K^T of the current item has
 //     been issued and completed (barrier q_free), i.e. during the current item's last key tile and epilogue;
 //   * the MMA warp issues the next item's first S MMAs as soon as those tiles have landed, under the epilogue;
 //   * O is staged for its TMA store in a tile of its own (not in the Q tiles), and the next item's first P.V waits only
 //     until the epilogue has read O out of TMEM (barrier o_free).
-// A non-persistent CTA pays about 7 us per item for launch, the first loads, the pipeline fill and the epilogue, which is
-// 20 % of an average item at T = 4096 and half of one at T = 1024; here most of it runs under another item's work.
+// A CTA launched per item pays about 7 us for launch, the first loads, the pipeline fill and the epilogue (measured on
+// the one-CTA-per-item form this kernel replaced): 20 % of an average item at T = 4096 and half of one at T = 1024;
+// here most of it runs under another item's work.
 // All mbarrier phases run on from item to item; each role derives them from its own counters.
 // Items are drawn, not assigned: a CTA starts on item blockIdx.x and its TMA thread draws every further index from a
 // counter in global memory (ItemRing in sm100_ptx.cuh hands it to the other roles), so CTAs that drew short walks draw more
@@ -22,9 +22,9 @@
 
 namespace ib200 {
 
-template <int D_>
-struct FwdPersistTraits : FwdTraits<D_, false> {
-    using Base = FwdTraits<D_, false>;
+template <int D_, bool SPLIT_ = false>
+struct FwdPersistTraits : FwdTraits<D_, SPLIT_> {
+    using Base = FwdTraits<D_, SPLIT_>;
     static constexpr int OFF_STAGE = Base::SMEM_TILES * Base::TILE_BYTES;      // one O staging tile, used by both query tiles in turn
     static constexpr int OFF_BAR = OFF_STAGE + Base::TILE_BYTES;
     static constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024 /*align slack*/;
@@ -41,8 +41,10 @@ struct FwdPersistParams {
 
 template <class TR>
 __global__ void __launch_bounds__(TR::THREADS, 1)
-attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, FwdPersistParams pp) {
+attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_q_lo,
+                        const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_k_lo,
+                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_v_lo,
+                        const __grid_constant__ CUtensorMap tm_o, FwdPersistParams pp) {
     constexpr int D = TR::D, BM = TR::BM, BN = TR::BN, KS = TR::KV_STAGES;
     const FwdParams& prm = pp.p;
     extern __shared__ uint8_t smem_raw[];
@@ -106,7 +108,10 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         fence_mbar_init();
     }
     if (warp == 8) { tmem_alloc(tmem_slot, TR::TM_COLS); tmem_relinquish(); }
-    if (warp == 9 && lane == 0) { tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_o); }
+    if (warp == 9 && lane == 0) {
+        tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_o);
+        if constexpr (TR::SPLIT) { tma_prefetch_desc(&tm_q_lo); tma_prefetch_desc(&tm_k_lo); tma_prefetch_desc(&tm_v_lo); }
+    }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -128,10 +133,14 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 if (n > 0) mbar_wait(q_free, (n - 1) & 1, ab, 12);
                 const int q_tiles = (it.nkv1 > 0) ? 2 : 1;
                 mbar_arrive_expect_tx(q_full, (q_tiles + 1) * TR::TILE_BYTES);
-                for (int p = 0; p < TR::NP; ++p) tma_load_4d(sQ + p * TR::PANEL_BYTES, &tm_q, q_full, p * 64, it.m0 * BM, it.hd, it.bt);
+                // panel p of a tile: columns 64p.. of a bf16 operand, or (fp32 I/O) the hi / lo half of the bf16 pair
+                auto col = [](int p) { return TR::SPLIT ? 0 : p * 64; };
+                for (int p = 0; p < TR::NP; ++p) tma_load_4d(sQ + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_q_lo : &tm_q, q_full, col(p), it.m0 * BM, it.hd, it.bt);
                 if (q_tiles == 2)
-                    for (int p = 0; p < TR::NP; ++p) tma_load_4d(sQ + TR::TILE_BYTES + p * TR::PANEL_BYTES, &tm_q, q_full, p * 64, it.m1 * BM, it.hd, it.bt);
-                for (int p = 0; p < TR::NP; ++p) tma_load_4d(sK + (G % KS) * TR::TILE_BYTES + p * TR::PANEL_BYTES, &tm_k, q_full, p * 64, 0, it.hd, it.bt);
+                    for (int p = 0; p < TR::NP; ++p)
+                        tma_load_4d(sQ + TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_q_lo : &tm_q, q_full, col(p), it.m1 * BM, it.hd, it.bt);
+                for (int p = 0; p < TR::NP; ++p)
+                    tma_load_4d(sK + (G % KS) * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_k_lo : &tm_k, q_full, col(p), 0, it.hd, it.bt);
                 idx = static_cast<int>(gridDim.x) + drawn;
                 item_ring_publish(ring, n, idx, ab);
                 for (int j = 0; j < it.n_iter; ++j, ++G) {
@@ -142,9 +151,10 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                     mbar_arrive_expect_tx(&kv_full[s], (has_k ? 2 : 1) * TR::TILE_BYTES);
                     if (has_k)
                         for (int p = 0; p < TR::NP; ++p)
-                            tma_load_4d(sK + ((G + 1) % KS) * TR::TILE_BYTES + p * TR::PANEL_BYTES, &tm_k, &kv_full[s], p * 64, (j + 1) * BN, it.hd, it.bt);
+                            tma_load_4d(sK + ((G + 1) % KS) * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_k_lo : &tm_k, &kv_full[s], col(p),
+                                        (j + 1) * BN, it.hd, it.bt);
                     for (int p = 0; p < TR::NP; ++p)
-                        tma_load_4d(sV + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, &tm_v, &kv_full[s], p * 64, j * BN, it.hd, it.bt);
+                        tma_load_4d(sV + s * TR::TILE_BYTES + p * TR::PANEL_BYTES, (TR::SPLIT && p) ? &tm_v_lo : &tm_v, &kv_full[s], col(p), j * BN, it.hd, it.bt);
                 }
             }
         }
@@ -184,10 +194,16 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                         if (j == 0 && oc[i] > 0) mbar_wait(&o_free[i], (oc[i] - 1) & 1, ab, 26);
                         mbar_wait(&p_half[2 * i], pc[i] & 1, ab, 24);
                         tc_fence_after_sync();
-                        fwd_issue_pv_part<TR, 0, TR::PV_KSTEPS / 2>(tm_o, tm_s, v_lo, j == 0, leader);
-                        mbar_wait(&p_half[2 * i + 1], pc[i] & 1, ab, 25);
-                        tc_fence_after_sync();
-                        fwd_issue_pv_part<TR, TR::PV_KSTEPS / 2, TR::PV_KSTEPS>(tm_o, tm_s, v_lo, j == 0, leader);
+                        if constexpr (!TR::SPLIT) {
+                            fwd_issue_pv_part<TR, 0, TR::PV_KSTEPS / 2>(tm_o, tm_s, v_lo, j == 0, leader);
+                            mbar_wait(&p_half[2 * i + 1], pc[i] & 1, ab, 25);
+                            tc_fence_after_sync();
+                            fwd_issue_pv_part<TR, TR::PV_KSTEPS / 2, TR::PV_KSTEPS>(tm_o, tm_s, v_lo, j == 0, leader);
+                        } else {
+                            mbar_wait(&p_half[2 * i + 1], pc[i] & 1, ab, 25);
+                            tc_fence_after_sync();
+                            fwd_issue_pv<TR>(tm_o, tm_s, v_lo, j == 0, leader);
+                        }
                         ++pc[i];
                         if (j + 1 < nkv[i]) {
                             fwd_issue_s<TR>(tm_s, q_lo[i], k_next_lo, leader);
@@ -284,14 +300,17 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
                 for (int cc = 0; cc < BN; cc += 32) {
-                    uint32_t pk[16];
+                    uint32_t pk[16], pl[16];
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
                         float x0, x1;
                         unpack_f32x2(ffma2(pack_f32x2(s[cc + e], s[cc + e + 1]), c2, nm2), x0, x1);
                         const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
                         acc2[(e >> 1) & 3] = fadd2(acc2[(e >> 1) & 3], pack_f32x2(p0, p1));
-                        pk[e >> 1] = pack_bf16x2(p0, p1);
+                        const uint32_t hi = pack_bf16x2(p0, p1);
+                        pk[e >> 1] = hi;
+                        if constexpr (TR::SPLIT)
+                            pl[e >> 1] = pack_bf16x2(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xffff0000u));
                     }
                     if (cc == BN / 2) {
                         // columns 0-63 were stored a chunk ago: publish them (the wait returns at once)
@@ -301,6 +320,7 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                         if (lane == 0) mbar_arrive(&p_half[2 * i]);
                     }
                     tmem_st_x16(tm_s + (cc >> 1), pk);
+                    if constexpr (TR::SPLIT) tmem_st_x16(tm_s + 64 + (cc >> 1), pl);
                 }
                 {
                     float a0, a1;
@@ -332,16 +352,30 @@ attn_fwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&o_free[i]);
                     }
-                    // 32 columns = 64 bytes = 4 chunks of 16 B inside panel cc/64
-                    const int panel = cc / 64, chunk0 = (cc % 64) / 8;
+                    if constexpr (!TR::SPLIT) {
+                        // 32 columns = 64 bytes = 4 chunks of 16 B inside panel cc/64
+                        const int panel = cc / 64, chunk0 = (cc % 64) / 8;
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint4 v;
-                        v.x = pack_bf16x2(__uint_as_float(r[q4 * 8 + 0]) * inv_l, __uint_as_float(r[q4 * 8 + 1]) * inv_l);
-                        v.y = pack_bf16x2(__uint_as_float(r[q4 * 8 + 2]) * inv_l, __uint_as_float(r[q4 * 8 + 3]) * inv_l);
-                        v.z = pack_bf16x2(__uint_as_float(r[q4 * 8 + 4]) * inv_l, __uint_as_float(r[q4 * 8 + 5]) * inv_l);
-                        v.w = pack_bf16x2(__uint_as_float(r[q4 * 8 + 6]) * inv_l, __uint_as_float(r[q4 * 8 + 7]) * inv_l);
-                        st_shared_sw128(sO + panel * TR::PANEL_BYTES, t, chunk0 + q4, v);
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            uint4 v;
+                            v.x = pack_bf16x2(__uint_as_float(r[q4 * 8 + 0]) * inv_l, __uint_as_float(r[q4 * 8 + 1]) * inv_l);
+                            v.y = pack_bf16x2(__uint_as_float(r[q4 * 8 + 2]) * inv_l, __uint_as_float(r[q4 * 8 + 3]) * inv_l);
+                            v.z = pack_bf16x2(__uint_as_float(r[q4 * 8 + 4]) * inv_l, __uint_as_float(r[q4 * 8 + 5]) * inv_l);
+                            v.w = pack_bf16x2(__uint_as_float(r[q4 * 8 + 6]) * inv_l, __uint_as_float(r[q4 * 8 + 7]) * inv_l);
+                            st_shared_sw128(sO + panel * TR::PANEL_BYTES, t, chunk0 + q4, v);
+                        }
+                    } else {
+                        // 32 fp32 columns = one 128-byte panel row = 8 chunks of 16 B
+                        const int panel = cc / 32;
+#pragma unroll
+                        for (int q4 = 0; q4 < 8; ++q4) {
+                            uint4 v;
+                            v.x = __float_as_uint(__uint_as_float(r[q4 * 4 + 0]) * inv_l);
+                            v.y = __float_as_uint(__uint_as_float(r[q4 * 4 + 1]) * inv_l);
+                            v.z = __float_as_uint(__uint_as_float(r[q4 * 4 + 2]) * inv_l);
+                            v.w = __float_as_uint(__uint_as_float(r[q4 * 4 + 3]) * inv_l);
+                            st_shared_sw128(sO + panel * TR::PANEL_BYTES, t, q4, v);
+                        }
                     }
                 }
                 if (row_g < T) prm.lse[static_cast<size_t>(it.bh) * T + row_g] = (m_used + log2f(l)) * 0.6931471805599453f;
