@@ -20,12 +20,32 @@ namespace {
     std::exit(1);
 }
 
-float* dev_ptr(const Tensor& t) { return GetImpl(t)->data_as_ptr<float>() + t.offset(); }
+// First element of the tensor (offset() counts elements of the tensor's own type).
+void* dev_ptr(const Tensor& t) {
+    auto impl = GetImpl(t);
+    return t.dtype() == DType::BFloat16 ? static_cast<void*>(impl->data_as_ptr<unsigned short>() + t.offset())
+                                        : static_cast<void*>(impl->data_as_ptr<float>() + t.offset());
+}
+float* dev_f32(const Tensor& t) { return static_cast<float*>(dev_ptr(t)); }
 
-// Scratch for the kernels, allocated like any other Inferno tensor (CUDAStorage = cudaMalloc RAII,
-// src/inferno/storage/cudastorage.cpp:16-23) and released when it goes out of scope.
-Tensor make_workspace(size_t bytes, const Device& dev) {
-    return Tensor(DType::Float32, std::vector<size_t>{bytes / 4 + 64}, "attention_ws", dev);
+// Scratch for the kernels: one Inferno tensor (CUDAStorage = cudaMalloc RAII, src/inferno/storage/cudastorage.cpp:16-23)
+// kept for the life of the process and grown on demand, so that a call neither allocates nor frees (cudaFree
+// synchronises the device) and the sticky status word in its header survives from call to call.  The reference is
+// single-threaded with one CUDA device (src/inferno/gradengine/engine.cpp:6), and so is this cache.
+// The holder is never destroyed: at process exit the reference's own bookkeeping statics (node tracker, id broker) may
+// already be gone when a Tensor destructor would reach for them.
+Tensor& workspace_tensor() {
+    static Tensor* t = new Tensor();
+    return *t;
+}
+size_t g_workspace_bytes = 0;
+void* workspace(size_t bytes, const Device& dev) {
+    if (bytes > g_workspace_bytes) {
+        causal_attention_check();                       // read the old buffer's status word before it goes
+        workspace_tensor() = Tensor(DType::Float32, std::vector<size_t>{bytes / 4 + 64}, "attention_ws", dev);
+        g_workspace_bytes = bytes;
+    }
+    return dev_ptr(workspace_tensor());
 }
 
 void check(int rc, const char* what) {
@@ -39,10 +59,21 @@ Tensor make_bf16_buffer(size_t n, const char* name, const Device& dev) {
 
 }  // namespace
 
+void causal_attention_check() {
+    if (g_workspace_bytes == 0) return;
+    int code = 0;
+    const int rc = ib200_attn_check(dev_ptr(workspace_tensor()), nullptr, &code);
+    if (rc != IB200_OK) fail(std::string(ib200_status_string(rc)) + " (device code " + std::to_string(code) + ")");
+}
+
 Tensor causal_attention(const Tensor& q_in, const Tensor& k_in, const Tensor& v_in, float scale, AttentionMath math) {
     if (q_in.device() != k_in.device() || q_in.device() != v_in.device()) fail("tensors are on different devices");
     if (q_in.ndim() != 4 || q_in.shape() != k_in.shape() || q_in.shape() != v_in.shape()) fail("expects q, k, v of equal shape [B, H, T, D]");
-    if (q_in.dtype() != DType::Float32 || k_in.dtype() != DType::Float32 || v_in.dtype() != DType::Float32) fail("expects Float32 tensors");
+    if (q_in.dtype() != k_in.dtype() || q_in.dtype() != v_in.dtype()) fail("q, k, v must have one dtype");
+    if (q_in.dtype() != DType::Float32 && q_in.dtype() != DType::BFloat16) fail("expects Float32 or BFloat16 tensors");
+    const bool native16 = q_in.dtype() == DType::BFloat16;      // the tensors' own storage is what the bf16 kernels read
+    if (native16 && !(q_in.is_contiguous() && k_in.is_contiguous() && v_in.is_contiguous()))
+        fail("BFloat16 tensors must be dense (contiguous() has no BFloat16 arm)");
 
     switch (q_in.device().m_type) {
         case DeviceType::CUDA: break;
@@ -56,11 +87,11 @@ Tensor causal_attention(const Tensor& q_in, const Tensor& k_in, const Tensor& v_
     const auto& shp = q.shape();
     const int B = static_cast<int>(shp[0]), H = static_cast<int>(shp[1]), T = static_cast<int>(shp[2]), D = static_cast<int>(shp[3]);
     const size_t n = q.numel();
-    const bool bf16 = math == AttentionMath::BFloat16;
-    const int dtype = bf16 ? IB200_DTYPE_BF16 : IB200_DTYPE_F32;
+    const bool bf16 = !native16 && math == AttentionMath::BFloat16;      // Float32 tensors through bf16 copies
+    const int dtype = (bf16 || native16) ? IB200_DTYPE_BF16 : IB200_DTYPE_F32;
 
     const bool gradreq = grad_enabled && (q_in.requires_grad() || k_in.requires_grad() || v_in.requires_grad());
-    Tensor out(DType::Float32, shp, "attention", q.device(), gradreq);
+    Tensor out(q.dtype(), shp, "attention", q.device(), gradreq);
     Tensor lse(DType::Float32, std::vector<size_t>{shp[0], shp[1], shp[2]}, "attention_lse", q.device());
 
     // what the kernels read and write: the tensors themselves, or bf16 copies of them
@@ -70,21 +101,19 @@ Tensor causal_attention(const Tensor& q_in, const Tensor& k_in, const Tensor& v_
         sk = make_bf16_buffer(n, "attention_k_bf16", q.device());
         sv = make_bf16_buffer(n, "attention_v_bf16", q.device());
         sout = make_bf16_buffer(n, "attention_out_bf16", q.device());
-        check(ib200_cast_f32_to_bf16(dev_ptr(q), dev_ptr(sq), n, nullptr), "cast q");
-        check(ib200_cast_f32_to_bf16(dev_ptr(k), dev_ptr(sk), n, nullptr), "cast k");
-        check(ib200_cast_f32_to_bf16(dev_ptr(v), dev_ptr(sv), n, nullptr), "cast v");
+        check(ib200_cast_f32_to_bf16(dev_f32(q), dev_ptr(sq), n, nullptr), "cast q");
+        check(ib200_cast_f32_to_bf16(dev_f32(k), dev_ptr(sk), n, nullptr), "cast k");
+        check(ib200_cast_f32_to_bf16(dev_f32(v), dev_ptr(sv), n, nullptr), "cast v");
     }
 
     size_t ws_bytes = 0;
     check(ib200_attn_workspace_bytes(B, H, T, D, dtype, IB200_PASS_FWD, &ws_bytes), "workspace query");
-    Tensor ws = make_workspace(ws_bytes, q.device());
+    void* ws = workspace(ws_bytes, q.device());
     // the reference launches everything on the legacy default stream
-    check(ib200_attn_fwd(dev_ptr(sq), dev_ptr(sk), dev_ptr(sv), dev_ptr(sout), dev_ptr(lse), B, H, T, D, scale, /*causal=*/1,
-                         dtype, IB200_MATH_SPLIT_BF16, dev_ptr(ws), ws_bytes, nullptr),
+    check(ib200_attn_fwd(dev_ptr(sq), dev_ptr(sk), dev_ptr(sv), dev_ptr(sout), dev_f32(lse), B, H, T, D, scale, /*causal=*/1,
+                         dtype, IB200_MATH_SPLIT_BF16, ws, g_workspace_bytes, nullptr),
           "forward");
-    if (bf16) check(ib200_cast_bf16_to_f32(dev_ptr(sout), dev_ptr(out), n, nullptr), "widen y");
-    int code = 0;
-    check(ib200_attn_check(dev_ptr(ws), nullptr, &code), "forward (device status)");
+    if (bf16) check(ib200_cast_bf16_to_f32(dev_ptr(sout), dev_f32(out), n, nullptr), "widen y");
 
     if (gradreq) GetImpl(out)->gradfn() = std::make_shared<AttentionBackward>(q_in, k_in, v_in, sq, sk, sv, sout, lse, scale, math);
     return out;
@@ -102,36 +131,36 @@ void AttentionBackward::backward() {
     const auto& shp = m_q.shape();
     const int B = static_cast<int>(shp[0]), H = static_cast<int>(shp[1]), T = static_cast<int>(shp[2]), D = static_cast<int>(shp[3]);
     const size_t n = m_q.numel();
-    const bool bf16 = m_math == AttentionMath::BFloat16;
-    const int dtype = bf16 ? IB200_DTYPE_BF16 : IB200_DTYPE_F32;
+    const bool native16 = m_q.dtype() == DType::BFloat16;
+    const bool bf16 = !native16 && m_math == AttentionMath::BFloat16;
+    const int dtype = (bf16 || native16) ? IB200_DTYPE_BF16 : IB200_DTYPE_F32;
     const Device dev = m_q.device();
-    // Float32 mode saved the inputs themselves; they may have been views, so make them dense again
+    if (g_out.dtype() != m_q.dtype()) fail("the upstream gradient must have the dtype of q, k, v");
+    // Float32 math saved the inputs themselves; they may have been views, so make them dense again
     Tensor sq = bf16 ? m_sq : m_sq.contiguous(), sk = bf16 ? m_sk : m_sk.contiguous(), sv = bf16 ? m_sv : m_sv.contiguous();
 
-    Tensor dq(DType::Float32, shp, "attention_dq", dev);
-    Tensor dk(DType::Float32, shp, "attention_dk", dev);
-    Tensor dv(DType::Float32, shp, "attention_dv", dev);
+    Tensor dq(m_q.dtype(), shp, "attention_dq", dev);
+    Tensor dk(m_q.dtype(), shp, "attention_dk", dev);
+    Tensor dv(m_q.dtype(), shp, "attention_dv", dev);
     Tensor sdo = g_out, sdq = dq, sdk = dk, sdv = dv;
     if (bf16) {
         sdo = make_bf16_buffer(n, "attention_do_bf16", dev);
         sdq = make_bf16_buffer(n, "attention_dq_bf16", dev);
         sdk = make_bf16_buffer(n, "attention_dk_bf16", dev);
         sdv = make_bf16_buffer(n, "attention_dv_bf16", dev);
-        check(ib200_cast_f32_to_bf16(dev_ptr(g_out), dev_ptr(sdo), n, nullptr), "cast dO");
+        check(ib200_cast_f32_to_bf16(dev_f32(g_out), dev_ptr(sdo), n, nullptr), "cast dO");
     }
     size_t ws_bytes = 0;
     check(ib200_attn_workspace_bytes(B, H, T, D, dtype, IB200_PASS_BWD, &ws_bytes), "workspace query");
-    Tensor ws = make_workspace(ws_bytes, dev);
-    check(ib200_attn_bwd(dev_ptr(sq), dev_ptr(sk), dev_ptr(sv), dev_ptr(m_sout), dev_ptr(sdo), dev_ptr(m_lse), dev_ptr(sdq), dev_ptr(sdk),
-                         dev_ptr(sdv), B, H, T, D, m_scale, 1, dtype, IB200_MATH_SPLIT_BF16, dev_ptr(ws), ws_bytes, nullptr),
+    void* ws = workspace(ws_bytes, dev);
+    check(ib200_attn_bwd(dev_ptr(sq), dev_ptr(sk), dev_ptr(sv), dev_ptr(m_sout), dev_ptr(sdo), dev_f32(m_lse), dev_ptr(sdq), dev_ptr(sdk),
+                         dev_ptr(sdv), B, H, T, D, m_scale, 1, dtype, IB200_MATH_SPLIT_BF16, ws, g_workspace_bytes, nullptr),
           "backward");
     if (bf16) {
-        check(ib200_cast_bf16_to_f32(dev_ptr(sdq), dev_ptr(dq), n, nullptr), "widen dq");
-        check(ib200_cast_bf16_to_f32(dev_ptr(sdk), dev_ptr(dk), n, nullptr), "widen dk");
-        check(ib200_cast_bf16_to_f32(dev_ptr(sdv), dev_ptr(dv), n, nullptr), "widen dv");
+        check(ib200_cast_bf16_to_f32(dev_ptr(sdq), dev_f32(dq), n, nullptr), "widen dq");
+        check(ib200_cast_bf16_to_f32(dev_ptr(sdk), dev_f32(dk), n, nullptr), "widen dk");
+        check(ib200_cast_bf16_to_f32(dev_ptr(sdv), dev_f32(dv), n, nullptr), "widen dv");
     }
-    int code = 0;
-    check(ib200_attn_check(dev_ptr(ws), nullptr, &code), "backward (device status)");
 
     // send gradients upstream (same pattern as MultiplyBackward::backward, src/inferno/gradfn/multiplybackward.cpp:34-57)
     auto nq = GetImpl(m_q)->grad_edge();

@@ -2,8 +2,11 @@
 // the reference's own headers and objects, run on Device::cuda(0), and its gradients are produced by the
 // reference's autograd Engine walking the AttentionBackward node (seeded through a multiply, because
 // Engine::backward always seeds ones, src/inferno/gradengine/engine.cpp:59).
-// Usage: shim_check B H T D q.bin k.bin v.bin do.bin out_prefix [bf16]   -> writes <prefix>.{o,dq,dk,dv}.bin
-// With the trailing "bf16" the op runs in AttentionMath::BFloat16 (Float32 tensors, bf16 kernels).
+// Usage: shim_check B H T D q.bin k.bin v.bin do.bin out_prefix [bf16 | native16]   -> writes <prefix>.{o,dq,dk,dv}.bin
+// With the trailing "bf16" the op runs in AttentionMath::BFloat16 (Float32 tensors, bf16 kernels).  With "native16"
+// q, k, v are converted to BFloat16 TENSORS first (to_dtype, a graph op with its own backward node), the op receives
+// those and hands their storage to the kernels, and its BFloat16 output is converted back for the loss: the Engine
+// walks MultiplyBackward -> CastBackward -> AttentionBackward -> CastBackward x3.
 #include <cstdio>
 #include <cstdlib>
 #include <string>
@@ -13,6 +16,7 @@
 #include "inferno/core/ops_impl.h"
 #include "inferno/core/tensorimpl.h"
 
+#include "../inferno_b200/inferno_shim/bf16_dtype.h"
 #include "../inferno_b200/inferno_shim/causal_attention.h"
 
 using Inferno::Tensor;
@@ -46,8 +50,18 @@ int main(int argc, char** argv) {
     Tensor dO(Inferno::DType::Float32, hdo, {B, H, T, D}, "dO", dev, false);
 
     const bool bf16 = argc > 10 && std::string(argv[10]) == "bf16";
-    Tensor y = Inferno::causal_attention(q, k, v, 1.0f / std::sqrt(static_cast<float>(D)),
-                                         bf16 ? Inferno::AttentionMath::BFloat16 : Inferno::AttentionMath::Float32);
+    const bool native16 = argc > 10 && std::string(argv[10]) == "native16";
+    const float scale = 1.0f / std::sqrt(static_cast<float>(D));
+    Tensor y;
+    if (native16) {
+        Tensor qb = Inferno::to_dtype(q, Inferno::DType::BFloat16), kb = Inferno::to_dtype(k, Inferno::DType::BFloat16),
+               vb = Inferno::to_dtype(v, Inferno::DType::BFloat16);
+        Tensor yb = Inferno::causal_attention(qb, kb, vb, scale);
+        if (yb.dtype() != Inferno::DType::BFloat16) { std::fprintf(stderr, "output is not BFloat16\n"); return 4; }
+        y = Inferno::to_dtype(yb, Inferno::DType::Float32);
+    } else {
+        y = Inferno::causal_attention(q, k, v, scale, bf16 ? Inferno::AttentionMath::BFloat16 : Inferno::AttentionMath::Float32);
+    }
     write_tensor(prefix + ".o.bin", y, n);
     Tensor loss = y * dO;          // MultiplyBackward hands dO to AttentionBackward
     loss.backward();
@@ -55,6 +69,7 @@ int main(int argc, char** argv) {
     write_tensor(prefix + ".dq.bin", q.Getgrad(), n);
     write_tensor(prefix + ".dk.bin", k.Getgrad(), n);
     write_tensor(prefix + ".dv.bin", v.Getgrad(), n);
+    Inferno::causal_attention_check();      // no bounded device-side wait expired in any of the calls above
     std::printf("shim_check ok\n");
     return 0;
 }

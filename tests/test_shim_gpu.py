@@ -56,6 +56,23 @@ def test_inferno_idiom_op_bf16_math(oracle_mod, shape):
         assert err < 2e-2, f"{name}: rel err {err:.3e}"
 
 
+@pytest.mark.parametrize("shape", [(1, 2, 200, 64), (2, 2, 384, 128)])
+def test_inferno_idiom_op_on_bfloat16_tensors(oracle_mod, shape):
+    """DType::BFloat16 tensors (the reference's dtype enum and dtype_size given one more entry): the op hands the tensors'
+    own storage to the bf16 kernels, returns a BFloat16 tensor, and the reference's Engine delivers BFloat16 gradients
+    through AttentionBackward; to_dtype (with its CastBackward node) sits either side only because the harness reads and
+    writes fp32 files.  The operands are bf16-representable, so nothing but the kernels' own rounding separates the
+    result from the float64 evaluation."""
+    if not os.path.isfile(SHIM):
+        pytest.skip("oracle/_ref/shim_check not built (reference sources absent at build time)")
+    q, k, v, do = make_inputs(*shape, 47, 1.0, 0.5, "bf16")
+    outs = run_binary(SHIM, [], q, k, v, do, tail=["native16"])
+    refs = oracle_mod.attn_fp64(q, k, v, do)
+    for name, x, r in zip(("O", "dQ", "dK", "dV"), outs, refs):
+        err = oracle_mod.rel_err(x, r)
+        assert err < 2e-2, f"{name}: rel err {err:.3e}"
+
+
 def test_against_the_reference_cuda_path(oracle_mod):
     """The reference's own composed CUDA path (cuBLAS SGEMM + its SIMT kernels, compiled for sm_100a) on
     configuration 1, against this library through the C ABI."""
