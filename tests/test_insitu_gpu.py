@@ -38,6 +38,35 @@ def test_insitu_timing_harness_runs():
     assert out["attn_fwd_ms"] > 0 and out["attn_bwd_main_ms"] > 0 and 0 < out["attn_share_of_step"] < 1
 
 
+def test_full_variant_matches_torch_composition():
+    """Packed attention plus the library's own projection GEMMs inside the model, against the plain PyTorch composition
+    with the same weights: loss, and the gradient of the first block's Wqkv (which has passed through W_out's backward,
+    the packed attention backward and Wqkv's own weight-gradient GEMM)."""
+    from inferno_b200.insitu_gpt import GPT
+    torch.manual_seed(1)
+    dev = torch.device("cuda")
+    cfg = dict(vocab=512, T=256, C=128, H=2, layers=2)
+    full = GPT(attn_impl="ib200_full", **cfg).to(dev).to(torch.bfloat16)
+    ref = GPT(attn_impl="torch", **cfg).to(dev).to(torch.bfloat16)
+    sd = full.state_dict()
+    for name in list(sd):          # this library's Linear stores its weight [in, out] (as the reference does), torch's [out, in]
+        if name.endswith(("wqkv.weight", "wout.weight")):
+            sd[name] = sd[name].t().contiguous()
+    ref.load_state_dict(sd)
+    idx = torch.randint(0, cfg["vocab"], (2, cfg["T"]), device=dev)
+    tgt = torch.randint(0, cfg["vocab"], (2, cfg["T"]), device=dev)
+    losses, grads = [], []
+    for m in (full, ref):
+        loss = torch.nn.functional.cross_entropy(m(idx).float().view(-1, cfg["vocab"]), tgt.view(-1))
+        loss.backward()
+        losses.append(float(loss.detach()))
+        g = m.blocks[0].wqkv.weight.grad.float()
+        grads.append(g if m is full else g.t())
+    assert abs(losses[0] - losses[1]) < 2e-2
+    rel = (grads[0] - grads[1]).norm() / grads[1].norm()
+    assert rel < 5e-2, f"Wqkv gradient differs by {rel:.3e}"
+
+
 def test_full_variant_trains():
     """Packed attention plus the library's own projection GEMMs inside the training step."""
     from inferno_b200.insitu_gpt import GPT, train_step
