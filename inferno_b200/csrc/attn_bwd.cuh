@@ -24,7 +24,7 @@
 // by a TMA reduction (cp.reduce.async.bulk.tensor .add), which keeps the adds off the
 // load/store pipe the compute warps depend on.
 //
-// Software pipeline of the MMA issuer inside an item (block = one 64-row query block, b = block & 1):
+// Software pipeline of the MMA issuer inside an item (block = one 64-row query block, b = block % NB; NB = 2 below):
 //   prologue   S^T(0) dP^T(0) S^T(1) dP^T(1)
 //   phase it   dQ^T(it) dK(it) dV(it) | S^T(it+2) dP^T(it+2)
 // so the compute warps work on block it+1 while the tensor pipe runs phase it, and the
@@ -59,7 +59,12 @@ struct BwdTraits {
     static constexpr int Q_PANEL = BQ * 128, Q_TILE = NP * Q_PANEL;
     static constexpr int DS_PART = BKV * 128;                // [128 keys x 64 queries] bf16
     static constexpr int DS_TILE = (SPLIT ? 2 : 1) * DS_PART;
-    static constexpr int NS = 3;                             // Q/dO ring depth
+    // S^T / dP^T buffers in TMEM = query blocks in flight.  Head dim 128 fills the 512 columns with two; bf16 head dim 64
+    // leaves 128 columns over, which buy a third (the compute warps, not the tensor pipe, pace a block there, and with
+    // three blocks in flight their chain front -> P^T / dS^T -> back overlaps itself).  The split mode has the columns
+    // but not the shared memory for the fourth ring stage a third buffer needs.
+    static constexpr int NB = (D == 64 && !SPLIT) ? 3 : 2;
+    static constexpr int NS = NB + 1;                        // Q/dO ring depth: the blocks in flight plus the one being loaded
     static constexpr int NTERMS = SPLIT ? 3 : 1;
     static constexpr int OUT_TILE = SPLIT ? BKV * D * 4 : KV_TILE;   // dK / dV staging bytes
     static constexpr int OUT_PANELS = SPLIT ? 2 : D / 64;
@@ -67,7 +72,8 @@ struct BwdTraits {
     static constexpr uint32_t IDESC_ST = make_idesc(kFmtBF16, BKV, BQ, kMajorK, kMajorK);
     static constexpr uint32_t IDESC_DKV = make_idesc(kFmtBF16, BKV, D, kMajorK, kMajorMN);
     static constexpr uint32_t IDESC_DQ = make_idesc(kFmtBF16, D, BQ, kMajorMN, kMajorMN);
-    static constexpr uint32_t TM_ST = 0, TM_DP = 128, TM_DV = 256, TM_DK = 384, TM_COLS = 512;
+    static constexpr uint32_t TM_ST = 0, TM_DP = NB * 64, TM_DV = 2 * NB * 64, TM_DK = TM_DV + D, TM_COLS = 512;
+    static_assert(TM_DK + D <= TM_COLS, "TMEM budget");
     static constexpr int OFF_K = 0;
     static constexpr int OFF_V = OFF_K + KV_TILE;
     static constexpr int OFF_Q = OFF_V + KV_TILE;            // NS tiles

@@ -30,7 +30,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                         const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_do_lo,
                         const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
                         const __grid_constant__ CUtensorMap tm_dq, BwdParams prm, int n_items, int n_groups, int* next_item) {
-    constexpr int D = TR::D, BKV = TR::BKV, BQ = TR::BQ, NS = TR::NS;
+    constexpr int D = TR::D, BKV = TR::BKV, BQ = TR::BQ, NS = TR::NS, NB = TR::NB;
     constexpr bool SPLIT = TR::SPLIT;
     // groups of four queries (of the eight a compute thread handles per block) whose lse / delta values are fetched early;
     // measured on one GPU with the builds swapped in place: at D = 128 all 8 (+2 % at T >= 4096 over 6, -2.5 % at T = 1024), at
@@ -56,14 +56,14 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     uint64_t* kv_full = bars;               // [1]   K, V of an item
     uint64_t* qdo_full = bars + 1;          // [NS]  TMA: Q, dO tiles + staged lse/delta
     uint64_t* qdo_empty = qdo_full + NS;    // [NS]  MMA commit: block consumed
-    uint64_t* sdp_full = qdo_empty + NS;    // [2]   MMA commit: S^T of a block is in TMEM (dP^T follows: dp_full)
-    uint64_t* pds_full = sdp_full + 2;      // [2]   compute warps: P^T, dS^T written (TMEM + smem)
-    uint64_t* dq_full = pds_full + 2;       // [2]   MMA commit: dQ^T in TMEM (and the dS^T smem tile is free)
-    uint64_t* dq_empty = dq_full + 2;       // [2]   drain warps: dQ^T copied to registers
-    uint64_t* dkv_full = dq_empty + 2;      // [1]   MMA commit: every MMA of the item has completed (dK, dV final; K, V tiles free)
+    uint64_t* sdp_full = qdo_empty + NS;    // [NB]  MMA commit: S^T of a block is in TMEM (dP^T follows: dp_full)
+    uint64_t* pds_full = sdp_full + NB;     // [NB]  compute warps: P^T, dS^T written (TMEM + smem)
+    uint64_t* dq_full = pds_full + NB;      // [NB]  MMA commit: dQ^T in TMEM (and the dS^T smem tile is free)
+    uint64_t* dq_empty = dq_full + NB;      // [NB]  drain warps: dQ^T copied to registers
+    uint64_t* dkv_full = dq_empty + NB;     // [1]   MMA commit: every MMA of the item has completed (dK, dV final; K, V tiles free)
     uint64_t* dkv_free = dkv_full + 1;      // [1]   drain warps (4): dK, dV read out of TMEM
-    uint64_t* dp_full = dkv_free + 1;       // [2]   MMA commit: dP^T of a block is in TMEM
-    uint64_t* item_bars = dp_full + 2;    // [4]   item ring: full[2], empty[2]
+    uint64_t* dp_full = dkv_free + 1;       // [NB]  MMA commit: dP^T of a block is in TMEM
+    uint64_t* item_bars = dp_full + NB;     // [4]   item ring: full[2], empty[2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(item_bars + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const ItemRing items{item_bars, item_bars + 2, abort_flag + 1};
@@ -91,7 +91,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         *abort_flag = 0;
         mbar_init(kv_full, 1);
         for (int s = 0; s < NS; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < NB; ++b) {
             mbar_init(&sdp_full[b], 1); mbar_init(&dp_full[b], 1); mbar_init(&pds_full[b], 8);
             mbar_init(&dq_full[b], 1); mbar_init(&dq_empty[b], 4);
         }
@@ -162,14 +162,14 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         const uint32_t lQ0 = sdesc_lo(smem_u32(sQ), 16), lDO0 = sdesc_lo(smem_u32(sDO), 16);
         constexpr uint32_t kStage = TR::Q_TILE >> 4;                               // ring stage stride in descriptor units
         constexpr uint32_t kToMN = ((TR::Q_PANEL >> 4) << 16) - (1u << 16);        // K-major view -> MN-major view of a Q/dO stage
-        // S^T and dP^T of global block gb into buffer gb & 1; the dP^T buffer must have been drained of dQ^T(gb - 2)
+        // S^T and dP^T of global block gb into buffer gb % NB; the dP^T buffer must have been drained of dQ^T(gb - NB)
         auto issue_front = [&](uint32_t gb) {
-            const uint32_t b = gb & 1, s = gb % NS;
+            const uint32_t b = gb % NB, s = gb % NS;
             mbar_wait(&qdo_full[s], (gb / NS) & 1, ab, 21);
             tc_fence_after_sync();
             bwd_issue_kmajor<TR>(tmem + TR::TM_ST + b * 64, lK, lQ0 + s * kStage, leader);
             if (kSplitHandoff && leader) umma_commit(&sdp_full[b]);    // the compute warps start on the exponentials while dP^T is still to come
-            if (gb >= 2) { mbar_wait(&dq_empty[b], ((gb - 2) >> 1) & 1, ab, 24); tc_fence_after_sync(); }
+            if (gb >= NB) { mbar_wait(&dq_empty[b], ((gb - NB) / NB) & 1, ab, 24); tc_fence_after_sync(); }
             bwd_issue_kmajor<TR>(tmem + TR::TM_DP + b * 64, lV, lDO0 + s * kStage, leader);
             if (leader) umma_commit(kSplitHandoff ? &dp_full[b] : &sdp_full[b]);
         };
@@ -180,14 +180,15 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             const Item item = decode(idx);
             const int nblk = item.nblk;
             mbar_wait(kv_full, ni & 1, ab, 20);
-            issue_front(g0);
-            if (nblk > 1) issue_front(g0 + 1);
+#pragma unroll
+            for (int j = 0; j < NB; ++j)
+                if (j < nblk) issue_front(g0 + j);
             for (int it = 0; it < nblk; ++it) {
                 const uint32_t gb = g0 + it;
-                const uint32_t b = gb & 1, s = gb % NS;
+                const uint32_t b = gb % NB, s = gb % NS;
                 const uint32_t lQ_mn = lQ0 + s * kStage + kToMN, lDO_mn = lDO0 + s * kStage + kToMN;
                 const uint32_t t_st = tmem + TR::TM_ST + b * 64, t_dp = tmem + TR::TM_DP + b * 64;
-                mbar_wait(&pds_full[b], (gb >> 1) & 1, ab, 22);
+                mbar_wait(&pds_full[b], (gb / NB) & 1, ab, 22);
                 tc_fence_after_sync();
                 if constexpr (!SPLIT) {
                     bwd_issue_dq<TR>(t_dp, lK_mn, lDS, leader);                            // dQ^T over the consumed dP^T buffer
@@ -206,7 +207,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                     if (leader) umma_commit(&dq_full[b]);
                 }
                 if (leader) umma_commit(&qdo_empty[s]);
-                if (it + 2 < nblk) issue_front(gb + 2);
+                if (it + NB < nblk) issue_front(gb + NB);
             }
             if (leader) umma_commit(dkv_full);
             g0 += nblk;
@@ -231,7 +232,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 
             for (int it = 0; it < nblk; ++it) {
                 const uint32_t gb = g0 + it;
-                const int b = gb & 1, s = gb % NS, m = m0 + it;
+                const int b = gb % NB, s = gb % NS, m = m0 + it;
                 const float* v_lse = sVec + s * 2 * BQ + h * 32;
                 const float* v_del = v_lse + BQ;
                 const uint32_t t_st = tmem + TR::TM_ST + b * 64 + h * 32 + lane_base;
@@ -246,7 +247,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                     nl_pre[e4] = reinterpret_cast<const float4*>(v_lse)[e4];
                     nd_pre[e4] = reinterpret_cast<const float4*>(v_del)[e4];
                 }
-                mbar_wait(&sdp_full[b], (gb >> 1) & 1, ab, 31);
+                mbar_wait(&sdp_full[b], (gb / NB) & 1, ab, 31);
                 tc_fence_after_sync();
                 uint32_t sr[32], dr[32];
                 tmem_ld_x32(t_st, sr);
@@ -290,10 +291,11 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 if constexpr (SPLIT) tmem_st_x16(t_st + 16, pl);
                 // Phase two, once dP^T is there: dS^T = P^T o (dP^T - delta).
                 // The single dS^T shared-memory tile is free once dQ^T of the previous block (of this or the previous item) has
-                // completed (a second tile, which would fit exactly, was measured: no gain); at D = 128 that wait comes first.
-                if (kWaitDsEarly && gb >= 1) mbar_wait(&dq_full[(gb - 1) & 1], ((gb - 1) >> 1) & 1, ab, 32);
+                // completed (a second tile was measured at both head dims: no gain at D = 128, +2 % at D = 64 and T = 8192 but
+                // -1 % at T <= 1024); at D = 128 that wait comes first.
+                if (kWaitDsEarly && gb >= 1) mbar_wait(&dq_full[(gb - 1) % NB], ((gb - 1) / NB) & 1, ab, 32);
                 if constexpr (kSplitHandoff) {
-                    mbar_wait(&dp_full[b], (gb >> 1) & 1, ab, 34);
+                    mbar_wait(&dp_full[b], (gb / NB) & 1, ab, 34);
                     tc_fence_after_sync();
                 }
                 tmem_ld_x32(t_dp, dr);
@@ -319,7 +321,7 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                     tmem_st_x16(t_dp, dk);          // dP^T has been read into registers: its buffer takes {dS^T hi, lo}
                     tmem_st_x16(t_dp + 16, dl);
                 }
-                if (!kWaitDsEarly && gb >= 1) mbar_wait(&dq_full[(gb - 1) & 1], ((gb - 1) >> 1) & 1, ab, 32);
+                if (!kWaitDsEarly && gb >= 1) mbar_wait(&dq_full[(gb - 1) % NB], ((gb - 1) / NB) & 1, ab, 32);
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
                     st_shared_sw128(sDS, r, h * 4 + c4, make_uint4(dk[4 * c4], dk[4 * c4 + 1], dk[4 * c4 + 2], dk[4 * c4 + 3]));
@@ -349,8 +351,8 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             const Item item = decode(idx);
             for (int it = 0; it < item.nblk; ++it) {
                 const uint32_t gb = g0 + it;
-                const int b = gb & 1, m = item.m0 + it;
-                mbar_wait(&dq_full[b], (gb >> 1) & 1, ab, 40);
+                const int b = gb % NB, m = item.m0 + it;
+                mbar_wait(&dq_full[b], (gb / NB) & 1, ab, 40);
                 tc_fence_after_sync();
                 uint32_t r0[32], r1[32];
                 tmem_ld_x32(tmem + TR::TM_DP + b * 64 + lane_base, r0);
