@@ -61,6 +61,7 @@ def parse_args():
     ap.add_argument("--e2e-nbuf", type=int, default=3, help="device staging sets of the host pipeline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-validate", action="store_true")
+    ap.add_argument("--no-cuda-graph", action="store_true", help="skip the CUDA-graph replay measured for small configurations")
     ap.add_argument("--ref-cuda", action="store_true", help="also time the reference's own CUDA path (small fp32 configs only)")
     return ap.parse_args()
 
@@ -249,6 +250,8 @@ def cpu_baseline_object(cfg, steps: int, with_extras: bool):
     obj = dict(value=value, unit=UNIT, cores=cores, kind=kind, seconds=sum(secs),
                sample=f"{steps} pass(es) of {cores} heads, one per host core, each the first {T_s} positions of a T={cfg.T} "
                       f"D={cfg.D} causal head, fp32 (the reference has no bf16)")
+    # the whole configuration at this rate (extrapolated linearly in the head count; for a prefix sample also in T^2)
+    obj["extrapolated_full_config_seconds"] = cfg.flops() / (value * 1e12)
     if with_extras:
         v1, _, dt1 = cpu_sample(cfg, T_s, 1)
         obj["one_core"] = dict(value=v1, unit=UNIT, cores=1, seconds=dt1, sample=f"one head, first {T_s} positions, one core")
@@ -466,6 +469,36 @@ def run_ours(args, cfg):
     total_flops = cfg.flops()
     value = total_flops / (ms_step * 1e-3) / 1e12
 
+    # Small configurations (a step of a few hundred microseconds, five dependent launches): the same step replayed as one
+    # CUDA graph, which takes the per-launch gaps out.  Reported beside the stream-launched figure, not instead of it.
+    graph = None
+    if flush and not args.no_cuda_graph:
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()                                   # the side stream's own workspace, allocated before the capture
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            step()
+        gev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(K)]
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        for i in range(K):
+            flush_buf.fill_(i & 0xff)
+            gev[i][0].record()
+            g.replay()
+            gev[i][1].record()
+        torch.cuda.synchronize()
+        tg = torch.tensor([sum(a.elapsed_time(b) for a, b in gev) / K], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        graph = dict(ms_per_step=float(tg.item()), value=total_flops / (float(tg.item()) * 1e-3) / 1e12, unit=UNIT,
+                     what="the same forward + backward captured once into a CUDA graph and replayed (5 kernel nodes), L2 flushed between replays")
+
     validation = None
     if not args.no_validate:
         validation = validate(cfg, torch, dist, world, heads, host_in, (o, dq, dk, dv), 2e-2 if cfg.dtype == "bf16" else 1e-3)
@@ -480,7 +513,7 @@ def run_ours(args, cfg):
         if world > 1:
             dist.destroy_process_group()
         return
-    finish(args, cfg, world, n, T, D, K, W, preload_steps, value, ms_step, fwd_ms_max, bwd_ms_max, clocks, e2e, validation, dist)
+    finish(args, cfg, world, n, T, D, K, W, preload_steps, value, ms_step, fwd_ms_max, bwd_ms_max, clocks, e2e, validation, graph, dist)
 
 
 def measure_e2e(args, torch, dist, HostAttention, dev, world, n, T, D, tdt, hin, resident, barrier, total_flops):
@@ -525,7 +558,7 @@ def measure_e2e(args, torch, dist, HostAttention, dev, world, n, T, D, tdt, hin,
                 outputs_equal_resident=bool(same))
 
 
-def finish(args, cfg, world, n, T, D, K, W, preload_steps, value, ms_step, fwd_ms_max, bwd_ms_max, clocks, e2e, validation, dist):
+def finish(args, cfg, world, n, T, D, K, W, preload_steps, value, ms_step, fwd_ms_max, bwd_ms_max, clocks, e2e, validation, graph, dist):
     pk = peaks()
     bf16 = cfg.dtype == "bf16"
     mma_per_product = 1 if bf16 else 3
@@ -533,6 +566,8 @@ def finish(args, cfg, world, n, T, D, K, W, preload_steps, value, ms_step, fwd_m
     bwd_flops_rank = 5.0 * n * float(T) ** 2 * D
     achieved = bwd_flops_rank / (bwd_ms_max * 1e-3) / 1e12
     mhz = clocks.get("sm_mhz_min_over_ranks") or clocks.get("sm_mhz")
+    e = 2 if bf16 else 4
+    hbm_bytes = 13.0 * cfg.B * cfg.H * T * D * e + 16.0 * cfg.B * cfg.H * T
     bwd_kernel = f"attn_bwd_persist_kernel<D={D}>" if bf16 else f"attn_bwd_persist_kernel<D={D}, split-bf16>"
     line = dict(
         metric=metric_name(cfg), value=value, unit=UNIT, n_gpus=world, steps=K, warmup=W, ms_per_step=ms_step,
@@ -548,8 +583,14 @@ def finish(args, cfg, world, n, T, D, K, W, preload_steps, value, ms_step, fwd_m
         bwd_main=dict(ms=bwd_ms_max, tflops=achieved),
         frac_of_bf16_peak=dict(value=value / world / peak, peak_tflops=peak,
                                of=pk["source"] + " sustained cuBLAS bf16" + ("" if bf16 else " / 3 (three bf16 MMAs per product)"),
-                               nominal_frac=value / world / (2250.0 / mma_per_product)),
+                               nominal_frac=value / world / (2250.0 / mma_per_product),
+                               **({} if bf16 else {"frac_of_nominal_tf32_peak": value / world / 1100.0})),
+        hbm=dict(compulsory_bytes_per_step=hbm_bytes, achieved_gbs=hbm_bytes / (ms_step * 1e-3) / 1e9 / world,
+                 frac_of_peak=hbm_bytes / (ms_step * 1e-3) / 1e9 / world / pk["hbm_gbs"], peak_gbs=pk["hbm_gbs"], of=pk["source"],
+                 note="13*N*e + 16*BH*T bytes (Q, K, V, dO, O in; O, dQ, dK, dV, lse out; delta pre-pass) over the step time, per GPU: "
+                      "far below the HBM rate, i.e. the step is compute-bound"),
         clocks=clocks,
+        cuda_graph=graph,
         validation=validation,
         e2e=e2e,
         gpu_launches=5 * K,
