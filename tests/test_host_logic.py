@@ -148,3 +148,31 @@ def test_bench_validation_digest_does_not_depend_on_the_rank_count(oracle_mod):
     a, b = make_head_inputs(cfg, 4), make_head_inputs(cfg, 4)
     assert all(np.array_equal(x, y) for x, y in zip(a, b))
     assert not np.array_equal(make_head_inputs(cfg, 3)[0], a[0])
+
+
+def test_bench_line_carries_the_contract_keys(capsys):
+    """The JSON line bench.py prints: every key the measurement contract names is present and consistent (built here from
+    made-up timings; no GPU involved)."""
+    import json
+    import types
+    import bench
+    from inferno_b200.synth import CONFIGS
+    cfg = CONFIGS["c5"]
+    args = types.SimpleNamespace(min_load_seconds=2.0, no_cpu_baseline=True, ref_cuda=False)
+    clocks = dict(sm_mhz=1560.0, sm_max_mhz=1965.0, reasons=["sw_power_cap"], samples=100, sm_mhz_min_over_ranks=1560.0)
+    e2e = dict(value=150.0, unit=bench.UNIT, h2d_bytes_per_step=4 << 30, d2h_bytes_per_step=4 << 30)
+    ms_step = 17.9
+    value = cfg.flops() / (ms_step * 1e-3) / 1e12
+    bench.finish(args, cfg, 1, cfg.B * cfg.H, cfg.T, cfg.D, 20, 5, 100, value, ms_step, 4.2, 12.4, clocks, e2e,
+                 dict(ok=True, checksum="0" * 16), None, None)
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "clocks", "e2e", "gpu_launches", "roofline", "validation", "hbm"):
+        assert key in line, key
+    assert line["steps"] == 20 and line["warmup"] == 5 and line["n_gpus"] == 1 and line["higher_is_better"] is True
+    assert line["vs_baseline"] is None and line["dtype"] == "bf16" and "workload" in line["config"] and "model" not in line["config"]
+    assert abs(line["value"] * line["ms_per_step"] * 1e-3 * 1e12 - cfg.flops()) / cfg.flops() < 1e-9
+    r = line["roofline"]
+    assert r["bound"] == "tensor" and r["unit"] == "TFLOP/s" and abs(r["frac"] - r["achieved"] / r["peak"]) < 1e-12
+    assert abs(r["achieved"] - 5.0 * cfg.B * cfg.H * cfg.T ** 2 * cfg.D / 12.4e-3 / 1e12) < 1e-6
+    assert line["gpu_launches"] == 5 * 20 and len(line["kernels_per_step"]) == 5
