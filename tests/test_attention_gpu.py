@@ -171,6 +171,28 @@ def test_config5_shape_replicated_heads(oracle_mod):
     assert_close([np_(o), np_(dq), np_(dk), np_(dv)], refs, TOL["bf16"], oracle_mod, "c5 prototypes")
 
 
+@pytest.mark.parametrize("dt,D", [("bf16", 128), ("bf16", 64), ("f32", 64)])
+def test_linearity_in_dO_and_causal_prefix_at_bench_length(dt, D):
+    """Size-independent properties at T = 4096 (the bench's sequence length), no checker needed.
+    (1) The backward is linear in dO: with 2 * dO every partial product doubles exactly (a power of two commutes with every
+        rounding), so dK and dV double bit for bit, and dQ up to the order of its floating-point reduction.
+    (2) A causal prefix is a self-contained sub-problem: O and lse of the first 2048 positions, computed from a T = 2048
+        call, equal the first 2048 rows of the T = 4096 call bit for bit (the same tiles are walked in the same order)."""
+    B, H, T = 2, 3, 4096
+    q, k, v, do = (torch.from_numpy(a).cuda().to(TDT[dt]) for a in make_inputs(B, H, T, D, 55, 1.0, 0.25, dt))
+    o, lse = A.attention_forward(q, k, v)
+    dq, dk, dv = A.attention_backward(q, k, v, o, do, lse)
+    dq2, dk2, dv2 = A.attention_backward(q, k, v, o, do * 2, lse)
+    torch.cuda.synchronize()
+    A.check_device_status()
+    assert torch.equal(dk2, dk * 2) and torch.equal(dv2, dv * 2)
+    assert (dq2.float() - 2 * dq.float()).norm() / dq.float().norm() < 1e-3
+    Tp = 2048
+    op, lsep = A.attention_forward(q[:, :, :Tp].contiguous(), k[:, :, :Tp].contiguous(), v[:, :, :Tp].contiguous())
+    torch.cuda.synchronize()
+    assert torch.equal(op, o[:, :, :Tp]) and torch.equal(lsep, lse[:, :, :Tp])
+
+
 def _torch_fp32_reference(q, k, v, do):
     """Causal attention and its gradients in plain fp32 torch ops on the GPU (scores materialised)."""
     q, k, v, do = (t.float() for t in (q, k, v, do))
