@@ -603,6 +603,16 @@ def finish(args, cfg, world, n, T, D, K, W, preload_steps, value, ms_step, fwd_m
                       traffic_source="ncu capture of one launch of this kernel on B=2 H=16 T=8192 D=128 (dram__bytes_read.sum + "
                                      "dram__bytes_write.sum), scaled by elements per launch; not measured in this run"),
     )
+    if bf16 and D == 128 and mhz:
+        # The tile shape's own ceiling: a 64-row query block of the backward moves 288 KB through shared memory (176 KB of MMA
+        # operand reads, 32 KB of TMA fills, 16 KB of dS^T, 64 KB of dQ^T staging in and out) for 5 x 2 x 128 x 64 x 128 flop,
+        # and an SM's shared memory carries 128 bytes per clock.
+        sms, block_flops, block_cycles = 148, 5.0 * 2 * 128 * 64 * 128, 288.0 * 1024 / 128
+        ceiling = block_flops * sms * mhz * 1e6 / block_cycles / 1e12
+        line["roofline"]["shared_memory_ceiling"] = dict(
+            tflops=ceiling, frac=achieved / ceiling,
+            note="what this tiling could reach at the sampled SM clock if a block took exactly its 288 KB / (128 B/clk) = 2304 cycles; "
+                 "causal-adjusted flops count the two diagonal blocks of an item at half, so 0.97 is the most a T = 4096 run can show")
     if world == 1 and not args.no_cpu_baseline:
         try:
             line["cpu_baseline"] = cpu_baseline_object(cfg, steps=6, with_extras=True)
