@@ -629,10 +629,10 @@ def finish(args, cfg, world, n, T, D, K, W, preload_steps, value, ms_step, fwd_m
 
 
 # DRAM bytes (read + write) of one attn_bwd_persist_kernel launch per element of a [heads, T, D] operand, from an ncu
-# capture of one launch on B=2 H=16 T=8192 D=128: (408.2 + 230.3) MB over 32 heads x 8192 x 128 elements.  DRAM traffic
+# capture of one launch on B=2 H=16 T=8192 D=128: (410.2 + 226.9) MB over 32 heads x 8192 x 128 elements.  DRAM traffic
 # of this kernel is proportional to the elements it touches (each operand is read once from DRAM; re-reads by other
 # CTAs of a head hit L2).
-TRAFFIC_BYTES_PER_ELEMENT = (408.220928e6 + 230.287872e6) / (32 * 8192 * 128)
+TRAFFIC_BYTES_PER_ELEMENT = (410.226688e6 + 226.940928e6) / (32 * 8192 * 128)
 
 
 def main():
