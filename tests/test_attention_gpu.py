@@ -5,7 +5,6 @@ Tolerances (normwise relative error ||x - ref||_F / ||ref||_F on O, dQ, dK, dV):
 The reference path itself has no bf16; for bf16 cases the checkers consume the bf16-rounded
 inputs upcast to fp32.
 """
-import os
 
 import numpy as np
 import pytest

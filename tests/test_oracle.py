@@ -1,5 +1,4 @@
 """The CPU checkers against the reference's own outputs (golden vectors) and against each other."""
-import os
 
 import numpy as np
 import pytest

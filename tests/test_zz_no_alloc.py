@@ -8,7 +8,6 @@ the second call finds the first call's leftovers in the shared buffer -- and che
 against the regular `ib200_attn_bwd`.  It lives in a file of its own that pytest collects last, and
 it does not depend on anything the other tests leave behind.
 """
-import numpy as np
 import pytest
 import torch
 
