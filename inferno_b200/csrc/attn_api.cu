@@ -200,7 +200,7 @@ int launch_fwd_persist(const void* q, const void* q_lo, const void* k, const voi
 template <class TR>
 int launch_bwd_persist(const void* const q[2], const void* const k[2], const void* const v[2], const void* const dO[2],
                        const RowLayout& lq, const RowLayout& lk, const RowLayout& lv, const RowLayout& ldo, const RowLayout& ldk,
-                       const RowLayout& ldv, const float* nlse2, const float* ndelta, int T_pad, float* dq_acc, void* dk, void* dv,
+                       const RowLayout& ldv, const float* nlse2, const float* ndelta, int T_pad, float* dq_acc, float dq_scale, void* dk, void* dv,
                        int* status, long BH, int T, float scale, int causal, cudaStream_t stream) {
     CUtensorMap tq[2], tk[2], tv[2], tdo[2], tdk, tdv, tdq;
     for (int i = 0; i < (TR::SPLIT ? 2 : 1); ++i) {
@@ -236,6 +236,7 @@ int launch_bwd_persist(const void* const q[2], const void* const k[2], const voi
     prm.causal = causal;
     prm.scale = scale;
     prm.scale_log2 = scale * 1.4426950408889634f;
+    prm.dq_scale = dq_scale;
     const long items = static_cast<long>((T + TR::BKV - 1) / TR::BKV) * BH;
     if (items > 0x7fffffffL) return IB200_ERR_UNSUPPORTED;
     int dev = 0, sms = 148;
@@ -266,6 +267,11 @@ int launch_bwd_typed(const void* q, const void* k, const void* v, const void* o,
     const long N = BH * T * D;
     int* status = reinterpret_cast<int*>(ws);
     float* dq_acc = reinterpret_cast<float*>(ws + kHeaderBytes);
+    // fp32 I/O with a dense dQ: the partial tiles, scaled, are added straight into the caller's dQ (zeroed by the pre-pass),
+    // and no finish pass runs; otherwise they meet in the workspace's fp32 accumulator, which dq_finish_kernel scales and casts
+    const RowLayout dense = dense_layout(L.q.H, T, D);
+    const bool dq_direct = F32 && L.dq.sb == dense.sb && L.dq.sh == dense.sh && L.dq.st == dense.st;
+    if (dq_direct) dq_acc = static_cast<float*>(dq);
     uint8_t* after_acc = ws + kHeaderBytes + round_up(N * 4, 256);
     const int T_pad = pad64(T);
     const size_t vec_bytes = round_up(static_cast<size_t>(BH) * T_pad * 4, 256);
@@ -298,9 +304,9 @@ int launch_bwd_typed(const void* q, const void* k, const void* v, const void* o,
     }
     int rc = launch_bwd_prepass<D, F32>(job, BH, T, T_pad, stream);
     if (rc) return rc;
-    rc = launch_bwd_persist<BwdTraits<D, F32>>(qp, kp, vp, dop, lq, lk, lv, ldo, L.dk, L.dv, nlse2, ndelta, T_pad, dq_acc, dk, dv, status,
-                                               BH, T, scale, causal, stream);
-    if (rc) return rc;
+    rc = launch_bwd_persist<BwdTraits<D, F32>>(qp, kp, vp, dop, lq, lk, lv, ldo, L.dk, L.dv, nlse2, ndelta, T_pad, dq_acc,
+                                               dq_direct ? scale : 1.f, dk, dv, status, BH, T, scale, causal, stream);
+    if (rc || dq_direct) return rc;
     return launch_dq_finish<D, F32>(dq_acc, dq, scale, L.dq, BH, T, stream);
 }
 

@@ -97,6 +97,8 @@ struct BwdParams {
     int* status;
     int T, BH, H, causal;  // H: heads per batch entry (operand tensor maps are 4-D: column, token, head, batch)
     float scale, scale_log2;
+    float dq_scale;        // factor applied to every dQ^T partial before it is added: 1 when an fp32 accumulator is finished by
+                           // dq_finish_kernel, `scale` when the partials go straight into a dense fp32 dQ (fp32 I/O)
 };
 
 // TMEM column of the packed bf16 pair that starts k-step ks (16 queries) of a P^T / dS^T operand.

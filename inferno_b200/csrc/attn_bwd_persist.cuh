@@ -366,9 +366,9 @@ attn_bwd_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 asm volatile("bar.sync 3, 128;" ::: "memory");
                 if (lane_ok) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) stage[e * D + d] = __uint_as_float(r0[e]);
+                    for (int e = 0; e < 32; ++e) stage[e * D + d] = SPLIT ? __uint_as_float(r0[e]) * prm.dq_scale : __uint_as_float(r0[e]);
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) stage[(32 + e) * D + d] = __uint_as_float(r1[e]);
+                    for (int e = 0; e < 32; ++e) stage[(32 + e) * D + d] = SPLIT ? __uint_as_float(r1[e]) * prm.dq_scale : __uint_as_float(r1[e]);
                 }
                 fence_proxy_async_smem();
                 asm volatile("bar.sync 3, 128;" ::: "memory");
