@@ -112,7 +112,9 @@ int ib200_attn_bwd_strided(const void* q, const void* k, const void* v, const vo
  * M, N, K multiples of 8; bases 16-byte aligned.  Replaces cublas_mm_row_major + the broadcast add of the reference's
  * Linear::forward (src/inferno/modules/linear.cpp:99-106, src/inferno/cuda/cudamatmul.cu:1058-1112,
  * src/inferno/cuda/cudaadd.cu:20-142); a transposed operand costs a descriptor, not the copy the reference makes
- * (src/inferno/gradfn/mmbackward.cpp:77-80). */
+ * (src/inferno/gradfn/mmbackward.cpp:77-80).  An expired device-side wait of these kernels is recorded in the status
+ * word of the library's built-in buffer (ib200_attn_check_static); the first call on a device looks that buffer's
+ * address up once, so make it outside any stream capture. */
 int ib200_gemm_bf16(const void* a, const void* b, void* c, const float* bias, int M, int N, int K,
                     int a_transposed, int b_transposed, ib200_stream_t stream);
 
